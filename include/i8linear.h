@@ -1,0 +1,155 @@
+/*
+ * libi8linear — C ABI of the B200 (sm_100a) INT8 quantized-linear kernels.
+ *
+ * Every entry point
+ *   - takes plain device pointers, sizes and a CUDA stream handle (cudaStream_t passed as void*),
+ *   - allocates nothing, never synchronises the device, launches on the given stream,
+ *   - returns 0 on success or a negative I8L_ERR_* code; i8l_last_error() gives the text for the
+ *     calling thread's most recent failure.
+ * The library contains no CPU fallback: on a device that is not compute capability 10.x every
+ * launch entry point returns I8L_ERR_ARCH.
+ *
+ * "Reference" below is the jiaoch/Triton-INT8 project; file:line cites name the Python/Triton code a
+ * function replaces.  Tensors are row-major and contiguous; a leading batch dimension is folded into
+ * the rows.  All of rows/cols/M/N/K must be multiples of 128 (the reference has no masking either).
+ */
+#ifndef I8LINEAR_H_
+#define I8LINEAR_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Exported-symbol marker (the library is built with hidden default visibility). */
+#define I8L_API __attribute__((visibility("default")))
+
+#define I8L_OK 0
+#define I8L_ERR_SHAPE (-1)   /* a dimension is zero, negative, too large or not a multiple of 128 */
+#define I8L_ERR_ALIGN (-2)   /* a pointer is not 16-byte aligned */
+#define I8L_ERR_ARCH (-3)    /* current device is not sm_100 */
+#define I8L_ERR_CUDA (-4)    /* a CUDA runtime/driver call failed */
+#define I8L_ERR_TIMEOUT (-5) /* a bounded device-side wait gave up (see i8l_gemm status word) */
+#define I8L_ERR_ARG (-6)     /* unsupported combination of options / null pointer */
+
+/* Quantisation group of one scale. */
+#define I8L_GRAN_TILE128 0  /* one scale per 128x128 tile            (reference block_channel A/dY) */
+#define I8L_GRAN_GROUP128 1 /* one scale per (row, 128 contraction elements)                        */
+#define I8L_GRAN_ROW 2      /* one scale per row over the whole contraction axis (per token/channel)*/
+
+/* Arithmetic of scale and rounding.  x is bf16 widened to fp32, amax the group's max |x|. */
+#define I8L_QMODE_TRITON 0 /* amax=max(amax,1e-4); s=127/amax (IEEE); q=clamp(floor(x*s+.5),-128,127); stores 1/s.
+                              triton/block_channel_fwd32.py:101-129,160-192 */
+#define I8L_QMODE_RNE 1    /* s=rcp(max(amax,1e-4))*127; q=clamp(rint(x*s),-127,127); stores rcp(s).
+                              tilelang/block_channel_bwd.py:96-104, tilelang/block_channel_fwd.py:206-230 */
+#define I8L_QMODE_FUSED 2  /* s=127/(amax+1e-5); q=floor(x*s+.5); stores s (the GEMM divides).
+                              triton/fused_triton_fwd32.py:49-59, triton/fused_triton_bwd33.py:50-56 */
+#define I8L_QMODE_ROWRCP 3 /* s=rcp(max(amax,1e-4))*127; q=clamp(floor(x*s+.5),-128,127); stores amax/127.
+                              triton/double-channle_fwd32.py:157-160,132-135 */
+
+/* Walsh-Hadamard rotation applied (in fp32, result rounded to bf16) before quantisation,
+ * always along the contraction axis of the operand. */
+#define I8L_HAD_NONE 0
+#define I8L_HAD_128 128   /* independent 128-point transforms */
+#define I8L_HAD_FULL (-1) /* one transform over the whole (power-of-two) contraction axis; ROW only */
+
+/*
+ * Quantise x (bf16 [batch, rows, cols]) in 128x128 tiles read once from HBM.
+ *
+ * Two operands can be produced from the same read:
+ *   q  / scale   : the operand x itself, contraction axis = cols.  q is int8 [batch, rows, cols].
+ *                  scale: TILE128 -> fp32 [batch, rows/128, cols/128]; GROUP128 -> [batch, rows, cols/128].
+ *   qt / scale_t : the operand x^T (per batch), contraction axis = rows.  qt is int8 [batch, cols, rows].
+ *                  scale_t: TILE128 -> [batch, cols/128, rows/128]; GROUP128 -> [batch, cols, rows/128].
+ * Either pair may be NULL (not produced).  hadamard is I8L_HAD_NONE or I8L_HAD_128.
+ * Replaces triton_per_block_quant (triton/block_channel_fwd32.py:194-212,
+ * triton/block_channel_bwd33.py:122-138) and, through qt, the transposed copies a linear layer's
+ * dW = dY^T X needs.
+ */
+I8L_API int i8l_quant_tile(const void* x, int64_t batch, int64_t rows, int64_t cols, int gran, int qmode,
+                   int hadamard, int8_t* q, float* scale, int8_t* qt, float* scale_t, void* stream);
+
+/*
+ * Quantise each row of x (bf16 [rows, cols]) with one scale over the whole row.
+ * q int8 [rows, cols], scale fp32 [rows].  hadamard: NONE, 128 or FULL (cols a power of two,
+ * cols <= 32768).  Replaces triton_per_token_quant (triton/block_channel_fwd32.py:132-157) and
+ * triton_per_row_quant_2d/3d incl. the torch glue between their two passes
+ * (triton/double-channle_fwd32.py:140-175,229-266, triton/double_channel_bwd33.py:142-176).
+ */
+I8L_API int i8l_quant_row(const void* x, int64_t rows, int64_t cols, int qmode, int hadamard, int8_t* q,
+                  float* scale, void* stream);
+
+/*
+ * Quantise the transpose of x (bf16 [rows, cols]) with one scale per column of x: the operand is
+ * x^T [cols, rows], contraction axis = rows.  qt int8 [cols, rows], scale_t fp32 [cols].
+ * colmax_scratch: fp32 [cols] device scratch, overwritten.  hadamard: NONE only.
+ * No counterpart function in the reference: it is triton_per_token_quant applied to W^T, which a
+ * linear layer's dX = dY W needs (the reference would transpose on the host first).
+ */
+I8L_API int i8l_quant_col_t(const void* x, int64_t rows, int64_t cols, int qmode, int8_t* qt, float* scale_t,
+                    float* colmax_scratch, void* stream);
+
+/* Scale layouts understood by the GEMM. */
+#define I8L_ASCALE_TILE 0  /* a_scale fp32 [batch, M/128, K/128] */
+#define I8L_ASCALE_GROUP 1 /* a_scale fp32 [batch, M, K/128]     */
+#define I8L_BSCALE_CHANNEL 0 /* b_scale fp32 [N]  (shared B) or [batch, N]      : K-invariant        */
+#define I8L_BSCALE_TILE 1    /* b_scale fp32 [N/128, K/128] or [batch, N/128, K/128]                  */
+#define I8L_BSCALE_GROUP 2   /* b_scale fp32 [N, K/128]     or [batch, N, K/128]                      */
+
+#define I8L_GEMM_EXACT_ORDER 1 /* per K step evaluate (float(P)*a_s)*b_s then add, unfused: bit-equal to the
+                                  reference's fp32 result.  Without it the K-invariant factor is applied once
+                                  at the end and multiply-adds are fused (same int32 partials). */
+#define I8L_GEMM_DIVIDE 2      /* scales are multipliers s: acc += float(P) / (a_s*b_s)  (fused variants) */
+#define I8L_GEMM_OUT_F32 4     /* C is fp32 instead of bf16 */
+
+/*
+ * Block-scaled INT8 GEMM: for every 128-wide K block kb, P = A_q[:,kb] . B_q[:,kb]^T exactly in int32
+ * (tcgen05.mma kind::i8, TMEM accumulator), then acc_f32 += float(P) * a_scale * b_scale;
+ * C = bf16(acc * post_scale + bias).
+ *   a_q int8 [batch, M, K]; b_q int8 [N, K] (b_batched=0) or [batch, N, K] (b_batched=1);
+ *   bias bf16 [N] or NULL; C bf16 (or fp32) [batch, M, N];
+ *   status: device int32 word (zeroed by the caller) that receives a non-zero code if a bounded
+ *   wait inside the kernel gave up; may be NULL.
+ * Replaces triton_gemm / int8_gemm_kernel of triton/block_channel_fwd32.py:12-96 (TILE, CHANNEL),
+ * triton/block_channel_bwd33.py:8-84 (TILE, TILE, b_batched) and, with I8L_GEMM_DIVIDE and
+ * I8L_BSCALE_GROUP / TILE, the arithmetic of triton/fused_triton_fwd32.py:42-65 and
+ * triton/fused_triton_bwd33.py:43-58.
+ */
+I8L_API int i8l_gemm_block(const int8_t* a_q, const int8_t* b_q, const float* a_scale, const float* b_scale,
+                   int a_scale_kind, int b_scale_kind, int b_batched, const void* bias,
+                   float post_scale, void* c, int64_t batch, int64_t M, int64_t N, int64_t K,
+                   int flags, int32_t* status, void* stream);
+
+/*
+ * Row x column scaled INT8 GEMM: int32 accumulation over the whole K in TMEM, then
+ * C = bf16( bf16((float(acc) * a_scale[m]) * b_scale[n]) * post_scale + bias ).
+ * The intermediate bf16 rounding reproduces the reference, which stores the GEMM result as bf16
+ * and multiplies by 1/K afterwards (triton/double-channle_fwd32.py:58-59,284); with
+ * post_scale == 1 and no bias it is the identity.
+ *   a_scale fp32 [batch, M]; b_scale fp32 [N] or [batch, N].
+ * Replaces triton/double-channle_fwd32.py:11-90 and triton/double_channel_bwd33.py:11-87.
+ */
+I8L_API int i8l_gemm_rowcol(const int8_t* a_q, const int8_t* b_q, const float* a_scale, const float* b_scale,
+                    int b_batched, const void* bias, float post_scale, void* c, int64_t batch,
+                    int64_t M, int64_t N, int64_t K, int flags, int32_t* status, void* stream);
+
+/*
+ * Raw int32 accumulators, for parity checks.  per_block=0: out int32 [batch, M, N] = sum over all K.
+ * per_block=1: out int32 [batch, K/128, M, N], one partial product per 128-wide K block.
+ * No counterpart in the reference (its kernels never expose the integer partials).
+ */
+I8L_API int i8l_gemm_dump_i32(const int8_t* a_q, const int8_t* b_q, int b_batched, int32_t* out,
+                      int64_t batch, int64_t M, int64_t N, int64_t K, int per_block,
+                      int32_t* status, void* stream);
+
+/* Text of the calling thread's most recent error ("" if none). */
+I8L_API const char* i8l_last_error(void);
+
+/* Library version, e.g. 100 = 0.1.0 */
+I8L_API int i8l_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* I8LINEAR_H_ */

@@ -1,0 +1,260 @@
+"""GPU parity tests: every CUDA kernel, called through the C ABI, against the CPU oracle and the
+golden vectors produced by the reference's own kernels.  Integer outputs and scales must match
+bit for bit; bf16 results within 1e-2 relative Frobenius error (far tighter in practice)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from golden_inputs import make_inputs
+from oracle import ref_semantics as R
+
+pytestmark = pytest.mark.gpu
+
+if torch.cuda.is_available():
+    from triton_int8_b200 import _lib as L
+    from triton_int8_b200 import block_channel as BC
+    from triton_int8_b200 import double_channel as DC
+    from triton_int8_b200 import fused as FU
+    from triton_int8_b200 import kernels as K
+
+DEV = "cuda"
+TOL_BF16 = 1e-2  # relative Frobenius error allowed for bf16 outputs (north-star tolerance)
+
+
+def _golden(golden_dir, name):
+    return np.load(os.path.join(golden_dir, name + ".npz"))
+
+
+def _same(t: torch.Tensor, ref, what=""):
+    ref = torch.as_tensor(np.asarray(ref)) if not isinstance(ref, torch.Tensor) else ref
+    t = t.detach().cpu()
+    assert t.shape == ref.shape, f"{what}: shape {tuple(t.shape)} vs {tuple(ref.shape)}"
+    bad = (t != ref).sum().item()
+    assert bad == 0, f"{what}: {bad} of {t.numel()} entries differ"
+
+
+def _status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+def _randq(g, *shape):
+    return torch.randint(-127, 128, shape, generator=g, dtype=torch.int8)
+
+
+# ------------------------------------------------------------------------------ quantizers
+@pytest.mark.parametrize("case", ["small", "edge", "c1"])
+def test_quant_tile_and_token_match_reference(golden_dir, case):
+    a, w, b3 = make_inputs(case)
+    aq_ref, as_ref = R.quant_tile128(a)
+    q, s = BC.triton_per_block_quant(a.to(DEV))
+    _same(q, aq_ref, "tile int8"); _same(s, as_ref, "tile scale")
+    wq_ref, ws_ref = R.quant_token(w)
+    q, s = BC.triton_per_token_quant(w.to(DEV))
+    _same(q, wq_ref, "token int8"); _same(s, ws_ref, "token scale")
+    if case != "c1":
+        g = _golden(golden_dir, "block_channel_" + case)
+        _same(BC.triton_per_block_quant(a.to(DEV))[0], g["aq"], "tile int8 vs golden")
+        _same(BC.triton_per_block_quant(b3.to(DEV))[1], g["b_s_bwd"], "tile scale vs golden")
+
+
+@pytest.mark.parametrize("gran", ["tile", "group"])
+@pytest.mark.parametrize("mode", ["triton", "rne", "fused"])
+def test_quant_tile_modes_and_transposed_output(gran, mode):
+    g = torch.Generator().manual_seed(7)
+    x = (torch.randn(2, 256, 384, generator=g) * 3).to(torch.bfloat16)
+    x[0, :128, :128] = 0
+    x[1, 5, 200] = 40.0
+    G = L.GRAN_TILE128 if gran == "tile" else L.GRAN_GROUP128
+    Mo = {"triton": L.QMODE_TRITON, "rne": L.QMODE_RNE, "fused": L.QMODE_FUSED}[mode]
+    q, s, qt, st = K.quant_tile(x.to(DEV), G, Mo, 0, natural=True, transposed=True)
+
+    def oracle(t):
+        if mode == "triton":
+            return R.quant_tile128(t) if gran == "tile" else R.quant_rowgroup128(t)
+        if mode == "rne":
+            return R.quant_tile128_rne(t) if gran == "tile" else R.quant_rowgroup128_rne(t)
+        B, M, Kd = t.shape
+        v = t.float().view(B, M // 128, 128, Kd // 128, 128) if gran == "tile" else t.float().view(B, M, Kd // 128, 128)
+        am = v.abs().amax(dim=(2, 4) if gran == "tile" else 3, keepdim=True) + 1e-5
+        sc = torch.full_like(am, 127.0) / am
+        qq = torch.floor(v * sc + 0.5).to(torch.int8).view(B, M, Kd)
+        return qq, sc.view(B, M // 128, Kd // 128) if gran == "tile" else sc.view(B, M, Kd // 128)
+
+    q_ref, s_ref = oracle(x)
+    _same(q, q_ref, "natural int8"); _same(s, s_ref, "natural scale")
+    xt = x.transpose(1, 2).contiguous()
+    qt_ref, st_ref = oracle(xt)
+    _same(qt, qt_ref, "transposed int8"); _same(st, st_ref, "transposed scale")
+
+
+def test_quant_row_modes_and_col_t():
+    a, w, _ = make_inputs("dc_small")
+    q, s = DC.triton_per_row_quant_3d(a.to(DEV))
+    q_ref, s_ref = R.quant_row(a)
+    _same(q, q_ref, "row int8"); _same(s, s_ref, "row scale")
+    g = torch.Generator().manual_seed(11)
+    w = (torch.randn(384, 1280, generator=g) * 0.02).to(torch.bfloat16)   # K not a power of two
+    w[7] = 0
+    q, s = BC.triton_per_token_quant(w.to(DEV))
+    q_ref, s_ref = R.quant_token(w)
+    _same(q, q_ref); _same(s, s_ref)
+    q, s = BC.triton_per_token_quant(w.to(DEV), round="rne")
+    q_ref, s_ref = R.quant_token_rne(w)
+    _same(q, q_ref); _same(s, s_ref)
+    qt, st = K.quant_col_t(w.to(DEV), L.QMODE_TRITON)          # W^T per input channel, for dX
+    q_ref, s_ref = R.quant_token(w.t().contiguous())
+    _same(qt, q_ref, "col_t int8"); _same(st, s_ref.view(-1), "col_t scale")
+
+
+@pytest.mark.parametrize("kind", ["tile128", "row128", "rowfull"])
+def test_hadamard_fused_quantizers(kind):
+    g = torch.Generator().manual_seed(13)
+    if kind == "rowfull":
+        x = torch.randn(2, 128, 2048, generator=g).to(torch.bfloat16)
+        q, s = DC.triton_per_row_quant_3d(x.to(DEV), hadamard="full")
+        q_ref, s_ref = R.quant_row(R.hadamard(x))
+    elif kind == "row128":
+        x = (torch.randn(256, 640, generator=g) * 0.02).to(torch.bfloat16)
+        q, s = BC.triton_per_token_quant(x.to(DEV), hadamard=128)
+        q_ref, s_ref = R.quant_token(R.hadamard(x, 128))
+    else:
+        x = torch.randn(2, 256, 384, generator=g).to(torch.bfloat16)
+        q, s = BC.triton_per_block_quant(x.to(DEV), hadamard=128)
+        q_ref, s_ref = R.quant_tile128(R.hadamard(x, 128))
+    # same butterfly order as the oracle -> bit-equal; a different FWHT order could differ by 1 LSB on ties
+    _same(q, q_ref, "rotated int8"); _same(s, s_ref, "rotated scale")
+
+
+# ------------------------------------------------------------------------------ int32 accumulators
+@pytest.mark.parametrize("shape", [(1, 128, 128, 128), (1, 128, 256, 256), (2, 256, 384, 640),
+                                   (1, 2048, 4096, 512), (3, 128, 128, 1152)])
+@pytest.mark.parametrize("b_batched", [False, True])
+def test_gemm_int32_accumulators_bit_exact(shape, b_batched):
+    B, M, N, Kd = shape
+    g = torch.Generator().manual_seed(B * 1000 + M + N + Kd)
+    aq = _randq(g, B, M, Kd)
+    bq = _randq(g, B, N, Kd) if b_batched else _randq(g, N, Kd)
+    st = _status()
+    out = K.gemm_dump_i32(aq.to(DEV), bq.to(DEV), per_block=False, status=st)
+    assert st.item() == 0
+    _same(out, R.gemm_i32(aq, bq), "whole-K int32")
+    outb = K.gemm_dump_i32(aq.to(DEV), bq.to(DEV), per_block=True, status=st)
+    assert st.item() == 0
+    ref = torch.stack([R.gemm_i32(aq[:, :, k:k + 128].contiguous(), bq[..., k:k + 128].contiguous())
+                       for k in range(0, Kd, 128)], dim=1)
+    _same(outb, ref, "per-K-block int32")
+
+
+def test_gemm_int32_extreme_values():
+    """All operands at +-127/-128: partial sums reach 128*128*128 per K block, K*16129 overall."""
+    aq = torch.full((1, 128, 1024), -128, dtype=torch.int8)
+    bq = torch.full((256, 1024), -128, dtype=torch.int8)
+    bq[::2] = 127
+    out = K.gemm_dump_i32(aq.to(DEV), bq.to(DEV))
+    _same(out, R.gemm_i32(aq, bq))
+
+
+# ------------------------------------------------------------------------------ scaled GEMMs
+@pytest.mark.parametrize("case", ["small", "edge"])
+def test_block_channel_exact_mode_equals_reference_kernels(golden_dir, case):
+    g = _golden(golden_dir, "block_channel_" + case)
+    a, w, b3 = make_inputs(case)
+    aq, a_s = BC.triton_per_block_quant(a.to(DEV))
+    wq, w_s = BC.triton_per_token_quant(w.to(DEV))
+    c = BC.triton_gemm(aq, wq, a_s, w_s, out_dtype=torch.float32, exact=True)
+    _same(c, g["c_fwd"], "fwd fp32 vs reference kernel output")
+    bq, b_s = BC.triton_per_block_quant(b3.to(DEV))
+    c2 = BC.triton_gemm(aq, bq, a_s, b_s, out_dtype=torch.float32, exact=True)
+    _same(c2, g["c_bwd"], "bwd fp32 vs reference kernel output")
+    # default (fast) path: same integers, scale factors regrouped -> within tolerance, bf16 output
+    y = BC.fwd_32(a.to(DEV), w.to(DEV))
+    assert R.rel_fro(y.cpu().float(), torch.as_tensor(g["c_fwd"])) < TOL_BF16
+    y2 = BC.bwd_33(a.to(DEV), b3.to(DEV))
+    assert R.rel_fro(y2.cpu().float(), torch.as_tensor(g["c_bwd"])) < TOL_BF16
+    _same(BC.fwd_32(a.to(DEV), w.to(DEV), exact=True), torch.as_tensor(g["c_fwd"]).to(torch.bfloat16), "bf16 exact")
+
+
+def test_block_channel_config1_both_wordings():
+    """BASELINE config 1 (512x1024x1024, outlier columns): reference scaling (tile128, half up) and the
+    per-(row,128)/RNE wording, forward + dX + dW by composition of the two primitives."""
+    a, w, dy = make_inputs("c1")
+    x = a[0]
+    y_ref, dx_ref, dw_ref = R.linear_block_channel(x, w, dy[0])
+    xd, wd, dyd = x.to(DEV), w.to(DEV), dy[0].to(DEV)
+    y = BC.fwd_32(xd[None], wd)[0]
+    dx = BC.fwd_32(dyd[None], wd.t().contiguous())[0]
+    dw = BC.bwd_33(dyd.t().contiguous()[None], xd.t().contiguous()[None])[0]
+    for got, ref, name in ((y, y_ref, "Y"), (dx, dx_ref, "dX"), (dw, dw_ref, "dW")):
+        err = R.rel_fro(got.cpu().float(), ref.float())
+        assert err < TOL_BF16, f"{name}: rel fro {err}"
+    # row128 / rne wording
+    aq, a_s = R.quant_rowgroup128_rne(a)
+    wq, w_s = R.quant_token_rne(w)
+    ref = R.gemm_block_general(aq, wq, a_s, w_s.view(-1), 1, "channel").to(torch.bfloat16)
+    got = BC.fwd_32(xd[None], wd, scaling="row128", round="rne")
+    assert R.rel_fro(got.cpu().float(), ref.float()) < TOL_BF16
+    got_exact = BC.fwd_32(xd[None], wd, scaling="row128", round="rne", exact=True)
+    _same(got_exact, ref, "row128/rne exact bf16")
+
+
+def test_double_channel_matches_reference_kernels(golden_dir):
+    g = _golden(golden_dir, "double_channel_small")
+    a, w, b3 = make_inputs("dc_small")
+    aq, a_s = DC.triton_per_row_quant_3d(a.to(DEV))
+    wq, w_s = DC.triton_per_row_quant_2d(w.to(DEV))
+    _same(aq, g["aq"]); _same(a_s, g["a_s"]); _same(wq, g["wq"]); _same(w_s, g["w_s"])
+    _same(DC.triton_gemm(aq, wq, a_s, w_s, out_dtype=torch.float32), g["c_fwd"], "fwd fp32")
+    bq, b_s = DC.triton_per_row_quant_3d(b3.to(DEV))
+    _same(DC.triton_gemm(aq, bq, a_s, b_s, out_dtype=torch.float32), g["c_bwd"], "bwd fp32")
+    # whole pipeline incl. the rotation and the bf16 `C * 1/K` pass, against the oracle
+    _same(DC.fwd_32(a.to(DEV), w.to(DEV)), R.double_channel_fwd_32(a, w), "fwd_32 bf16")
+    _same(DC.bwd_33(a.to(DEV), b3.to(DEV)), R.double_channel_bwd_33(a, b3), "bwd_33 bf16")
+    _same(DC.fwd_32(a.to(DEV), w.to(DEV), hadamard=None), R.double_channel_fwd_32(a, w, use_hadamard=False))
+
+
+def test_fused_matches_reference_kernels(golden_dir):
+    g = _golden(golden_dir, "fused_small")
+    a, w, b3 = make_inputs("small")
+    _same(FU.fused_int8_gemm(a.to(DEV), w.to(DEV), out_dtype=torch.float32), g["c_fwd"], "fused fwd fp32")
+    _same(FU.fused_int8_gemm(a.to(DEV), b3.to(DEV), out_dtype=torch.float32), g["c_bwd"], "fused bwd fp32")
+    _same(FU.fwd_32(a.to(DEV), w.to(DEV)), torch.as_tensor(g["c_fwd"]).to(torch.bfloat16))
+
+
+def test_reference_acceptance_gate():
+    """calc_diff < 1e-3 against the bf16 product on N(0,1) inputs: the reference's own check
+    (triton/block_channel_fwd32.py:257-272 and siblings), at 2 x 1024^3."""
+    g = torch.Generator().manual_seed(3)
+    a = torch.randn(2, 1024, 1024, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(1024, 1024, generator=g).to(torch.bfloat16).to(DEV)
+    b3 = torch.randn(2, 1024, 1024, generator=g).to(torch.bfloat16).to(DEV)
+    ref_f = torch.matmul(a, w.t())
+    ref_b = torch.matmul(a, b3.transpose(1, 2))
+    for mod in (BC, DC, FU):
+        assert mod.calc_diff(mod.fwd_32(a, w), ref_f) < 1e-3
+        assert mod.calc_diff(mod.bwd_33(a, b3), ref_b) < 1e-3
+
+
+def test_bias_and_hadamard128_forward():
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(1, 256, 512, generator=g).to(torch.bfloat16)
+    w = (torch.randn(384, 512, generator=g) * 0.02).to(torch.bfloat16)
+    bias = (torch.randn(384, generator=g) * 0.01).to(torch.bfloat16)
+    y_ref, _, _ = R.linear_block_channel(x[0], w, torch.zeros(256, 384, dtype=torch.bfloat16), hadamard128=True, bias=bias)
+    y = BC.fwd_32(x.to(DEV), w.to(DEV), hadamard=128, bias=bias.to(DEV))[0]
+    assert R.rel_fro(y.cpu().float(), y_ref.float()) < TOL_BF16
+    y = BC.fwd_32(x.to(DEV), w.to(DEV), hadamard=128, bias=bias.to(DEV), exact=True)[0]
+    _same(y, y_ref, "hadamard128 + bias, exact order")
+
+
+# ------------------------------------------------------------------------------ error behaviour
+def test_errors_are_reported_not_swallowed():
+    from triton_int8_b200 import I8LError
+    x = torch.zeros(1, 100, 128, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(I8LError, match="SHAPE"):
+        BC.triton_per_block_quant(x)
+    with pytest.raises(ValueError):
+        BC.triton_per_block_quant(torch.zeros(1, 128, 128, dtype=torch.bfloat16))   # CPU tensor: no fallback
+    with pytest.raises(TypeError):
+        BC.triton_per_block_quant(torch.zeros(1, 128, 128, device=DEV))             # fp32 input

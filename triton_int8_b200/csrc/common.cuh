@@ -1,0 +1,102 @@
+// Shared helpers for libi8linear (sm_100a only).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/i8linear.h"
+
+namespace i8l {
+
+// Records printf-style text for i8l_last_error() (thread local) and returns `code`.
+int fail(int code, const char* fmt, ...);
+
+// I8L_OK when the current device is compute capability 10.x.
+int check_arch();
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+#define I8L_CUDA_OK(expr)                                                                  \
+  do {                                                                                     \
+    cudaError_t _e = (expr);                                                               \
+    if (_e != cudaSuccess)                                                                 \
+      return i8l::fail(I8L_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e));      \
+  } while (0)
+
+// ---------------------------------------------------------------- scale / rounding arithmetic
+// All operations are spelled with explicit round-to-nearest intrinsics so that the compiler can
+// neither contract x*s+0.5 into an FMA nor replace a division by a reciprocal: the int8 values
+// and the stored scales must equal the reference's bit for bit.
+
+template <int MODE>
+__device__ __forceinline__ void make_scale(float amax, float& s, float& stored) {
+  if (MODE == I8L_QMODE_TRITON) {
+    amax = amax > 1e-4f ? amax : 1e-4f;
+    s = __fdiv_rn(127.0f, amax);
+    stored = __fdiv_rn(1.0f, s);
+  } else if (MODE == I8L_QMODE_RNE) {
+    amax = fmaxf(amax, 1e-4f);
+    s = __fmul_rn(__frcp_rn(amax), 127.0f);
+    stored = __frcp_rn(s);
+  } else if (MODE == I8L_QMODE_FUSED) {
+    s = __fdiv_rn(127.0f, __fadd_rn(amax, 1e-5f));
+    stored = s;
+  } else {  // I8L_QMODE_ROWRCP
+    amax = fmaxf(amax, 1e-4f);
+    s = __fmul_rn(__frcp_rn(amax), 127.0f);
+    stored = __fdiv_rn(amax, 127.0f);
+  }
+}
+
+template <int MODE>
+__device__ __forceinline__ int quant1(float v, float s) {
+  float y = __fmul_rn(v, s);
+  if (MODE == I8L_QMODE_RNE) {
+    y = fminf(fmaxf(rintf(y), -127.0f), 127.0f);
+  } else {
+    y = floorf(__fadd_rn(y, 0.5f));
+    y = fminf(fmaxf(y, -128.0f), 127.0f);  // never active for FUSED: |x*s| < 127
+  }
+  return __float2int_rn(y);
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t b) { return __uint_as_float(b << 16); }
+
+__device__ __forceinline__ void unpack8(const uint4& u, float* v) {
+  v[0] = bf16_bits_to_float(u.x & 0xffffu); v[1] = __uint_as_float(u.x & 0xffff0000u);
+  v[2] = bf16_bits_to_float(u.y & 0xffffu); v[3] = __uint_as_float(u.y & 0xffff0000u);
+  v[4] = bf16_bits_to_float(u.z & 0xffffu); v[5] = __uint_as_float(u.z & 0xffff0000u);
+  v[6] = bf16_bits_to_float(u.w & 0xffffu); v[7] = __uint_as_float(u.w & 0xffff0000u);
+}
+
+__device__ __forceinline__ float round_to_bf16(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+// 128-point Walsh-Hadamard transform of a row segment held as 8 consecutive values in each of 16
+// consecutive lanes (lane & 15 selects the 8-wide chunk).  Butterfly spans double from 1 to 64,
+// the order the CPU oracle uses; fp32 adds commute, so the result is bit-equal to it.
+__device__ __forceinline__ void fwht128_lanes16(float* v, int lane) {
+#pragma unroll
+  for (int h = 1; h < 8; h <<= 1) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if ((j & h) == 0) {
+        float a = v[j], b = v[j | h];
+        v[j] = __fadd_rn(a, b);
+        v[j | h] = __fsub_rn(a, b);
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 1; m < 16; m <<= 1) {
+    const bool upper = (lane & m) != 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float p = __shfl_xor_sync(0xffffffffu, v[j], m);
+      v[j] = upper ? __fsub_rn(p, v[j]) : __fadd_rn(v[j], p);
+    }
+  }
+}
+
+}  // namespace i8l

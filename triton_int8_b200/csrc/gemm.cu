@@ -1,0 +1,551 @@
+// INT8 GEMMs on the 5th-generation tensor cores: tcgen05.mma kind::i8 with int32 accumulators in
+// tensor memory, operands staged by TMA into a 128B-swizzled shared-memory ring.
+//
+// One persistent CTA per SM, 384 threads:
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      tensor-memory allocator + MMA issuer (one elected lane)
+//   warps 2-3   idle (they complete the first warpgroup so register budgets can be rebalanced)
+//   warps 4-11  epilogue: warp%4 selects the 32 accumulator lanes (rows) a warp may read, the
+//               warpgroup (4-7 / 8-11) selects columns 0-127 / 128-255 of the 128x256 tile.
+// Tensor memory holds two 128x256 int32 accumulators (all 512 columns).  In block-scaled mode the
+// MMA warp alternates between them every 128-wide K block while the epilogue drains the other one
+// into fp32 registers (acc += float(P) * scale); in row x column mode a buffer holds a whole tile
+// and the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Every wait on an mbarrier is bounded in wall time; on expiry the CTA raises a shared abort flag,
+// reports through the status word and every role leaves its loop, so the kernel always terminates
+// and frees its tensor memory.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace i8l {
+
+constexpr int BM = 128, BN = 256, BK = 128;
+constexpr int STAGES = 4;
+constexpr int A_STAGE = BM * BK;  // bytes
+constexpr int B_STAGE = BN * BK;
+constexpr int THREADS = 384;
+constexpr int TMEM_COLS = 512;
+constexpr uint32_t STAGE_TX = A_STAGE + B_STAGE;
+constexpr int SMEM_DYN = STAGES * (A_STAGE + B_STAGE) + 1024;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+
+struct GemmParams {
+  const float* a_scale;
+  const float* b_scale;
+  const __nv_bfloat16* bias;
+  void* c;
+  int32_t* status;
+  int m_blocks;  // batch*M/128
+  int mpb;       // M/128 (m-blocks per batch)
+  int n_tiles;   // ceil(N/256)
+  int M, N, KB;  // KB = K/128
+  int a_kind, b_kind, b_batched;
+  int exact, divide, out_f32, dump;  // dump: 0 none, 1 whole-K int32, 2 per-K-block int32
+  int raster;
+  float post_scale;
+};
+
+// ------------------------------------------------------------------------------------------ PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ unsigned long long globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false when the abort flag is (or becomes) set.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer();
+  for (uint32_t spin = 0;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 63u) == 63u) {
+      if (*abort_flag) return false;
+      if (globaltimer() - t0 > limit_ns) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void named_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, rows of 128 bytes, 128-byte swizzle,
+// 8-row groups 1024 bytes apart (the layout TMA writes with CU_TENSOR_MAP_SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
+  uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;              // leading byte offset (unused with swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;    // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;              // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;              // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: D=s32, A=B=s8, both K-major, M=128, N=256, dense, no saturation.
+constexpr uint32_t IDESC_I8 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                              ((uint32_t)(BM >> 4) << 24);
+
+struct TileCoord {
+  int m_blk, n_tile;
+};
+__device__ __forceinline__ TileCoord tile_coord(int t, const GemmParams& p) {
+  const int per_group = p.raster * p.n_tiles;
+  const int g = t / per_group, local = t - g * per_group;
+  const int first = g * p.raster;
+  const int gsize = min(p.raster, p.m_blocks - first);
+  TileCoord tc;
+  tc.m_blk = first + local % gsize;
+  tc.n_tile = local / gsize;
+  return tc;
+}
+
+struct __align__(8) SharedCtl {
+  uint64_t full[STAGES], empty[STAGES], tfull[2], tempty[2], done;
+  uint32_t tmem_base;
+  int abort_flag;
+  float bscale[2][128];     // per-tile column scales of each epilogue warpgroup (CHANNEL)
+  float bstep[2][2][128];   // per-K-block column scales (GROUP), double buffered
+};
+
+// BLOCK: drain the accumulator every 128-wide K block (block-scaled); otherwise once per tile.
+template <bool BLOCK>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ SharedCtl ctl;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t smem_a = smem_base, smem_b = smem_base + STAGES * A_STAGE;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &ctl.abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&ctl.full[s]), 1);
+      mbar_init(smem_u32(&ctl.empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctl.tfull[b]), 1);
+      mbar_init(smem_u32(&ctl.tempty[b]), 8);  // one arrival per epilogue warp
+    }
+    mbar_init(smem_u32(&ctl.done), 1);
+    ctl.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl.tmem_base)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl.tmem_base;
+  const int total_tiles = p.m_blocks * p.n_tiles;
+  const int KB = p.KB;
+
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (warp == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t issued = 0, issued_ph = 0;  // bit s: a load into stage s is (or was) in flight, with parity
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const TileCoord tc = tile_coord(t, p);
+        const int a_row = tc.m_blk * BM;
+        const int b_row = (p.b_batched ? (tc.m_blk / p.mpb) * p.N : 0) + tc.n_tile * BN;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!(ok = mbar_wait(smem_u32(&ctl.empty[s]), ph ^ 1u, abort_flag))) break;
+          if (lane == 0) {
+            const uint32_t bar = smem_u32(&ctl.full[s]);
+            mbar_expect_tx(bar, STAGE_TX);
+            tma_load_2d(smem_a + s * A_STAGE, &map_a, bar, kb * BK, a_row);
+            tma_load_2d(smem_b + s * B_STAGE, &map_b, bar, kb * BK, b_row);
+          }
+          issued |= 1u << s;
+          issued_ph = (issued_ph & ~(1u << s)) | (ph << s);
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // let copies already in flight land before the CTA's shared memory is released
+        for (int k = 0; k < STAGES; ++k)
+          if (issued & (1u << k)) {
+            int dummy = 0;
+            mbar_wait(smem_u32(&ctl.full[k]), (issued_ph >> k) & 1u, &dummy, 100000000ull);
+          }
+      }
+    } else if (warp == 1) {
+      // ------------------------------------------------------------------ MMA issuer
+      int s = 0, ab = 0;
+      uint32_t ph = 0, aph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int kb = 0; kb < KB; ++kb) {
+          const bool drain_start = BLOCK || kb == 0, drain_end = BLOCK || kb == KB - 1;
+          if (drain_start) {
+            if (!(ok = mbar_wait(smem_u32(&ctl.tempty[ab]), aph ^ 1u, abort_flag))) break;
+          }
+          if (!(ok = mbar_wait(smem_u32(&ctl.full[s]), ph, abort_flag))) break;
+          tc_fence_after();
+          if (lane == 0) {
+            const uint64_t da = smem_desc(smem_a + s * A_STAGE), db = smem_desc(smem_b + s * B_STAGE);
+            const uint32_t d = tmem_base + ab * BN;
+#pragma unroll
+            for (int k4 = 0; k4 < BK / 32; ++k4)
+              tc_mma_i8(d, da + 2 * k4, db + 2 * k4, IDESC_I8, (k4 > 0 || !drain_start) ? 1u : 0u);
+            tc_commit(smem_u32(&ctl.empty[s]));
+            if (drain_end) tc_commit(smem_u32(&ctl.tfull[ab]));
+          }
+          __syncwarp();
+          if (drain_end) {
+            ab ^= 1;
+            if (ab == 0) aph ^= 1u;
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+      // all MMAs issued by this thread must have retired before tensor memory is freed
+      if (lane == 0) tc_commit(smem_u32(&ctl.done));
+      __syncwarp();
+      int dummy = 0;
+      mbar_wait(smem_u32(&ctl.done), 0, &dummy);
+    }
+  } else {
+    // -------------------------------------------------------------------- epilogue
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    const int q = warp & 3, wg = (warp - 4) >> 2;
+    const int tix = q * 32 + lane;  // row within the tile == thread index within the warpgroup
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    int ab = 0;
+    uint32_t aph = 0;
+    bool ok = true;
+    const bool fast_scalar = BLOCK && !p.exact && !p.divide && p.b_kind != I8L_BSCALE_GROUP && !p.dump;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const TileCoord tc = tile_coord(t, p);
+      const int batch = tc.m_blk / p.mpb;
+      const int64_t row = (int64_t)tc.m_blk * BM + tix;  // row in the folded [batch*M] space
+      const int col0 = tc.n_tile * BN + wg * 128;
+      const bool active = col0 < p.N;
+      const int64_t bcol0 = (int64_t)(p.b_batched ? batch : 0) * p.N + col0;  // first b_scale column index
+      if (BLOCK ? (p.b_kind == I8L_BSCALE_CHANNEL && !p.dump) : !p.dump) {
+        named_sync(1 + wg, 128);
+        ctl.bscale[wg][tix] = active ? __ldg(p.b_scale + bcol0 + tix) : 0.f;
+        named_sync(1 + wg, 128);
+      }
+      float acc[BLOCK ? 128 : 1];
+      if (BLOCK) {
+#pragma unroll
+        for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+      }
+      const int ndrain = BLOCK ? KB : 1;
+      for (int d = 0; d < ndrain; ++d) {
+        float sa = 1.f, sb = 1.f;
+        if (BLOCK && !p.dump) {
+          sa = p.a_kind == I8L_ASCALE_TILE ? __ldg(p.a_scale + (int64_t)tc.m_blk * KB + d)
+                                           : __ldg(p.a_scale + row * KB + d);
+          if (p.b_kind == I8L_BSCALE_TILE && active) sb = __ldg(p.b_scale + (bcol0 >> 7) * KB + d);
+          if (p.b_kind == I8L_BSCALE_GROUP) {
+            ctl.bstep[wg][d & 1][tix] = active ? __ldg(p.b_scale + (bcol0 + tix) * KB + d) : 0.f;
+            named_sync(1 + wg, 128);
+          }
+        }
+        if (!(ok = mbar_wait(smem_u32(&ctl.tfull[ab]), aph, abort_flag))) break;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + lane_addr + ab * BN + wg * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          if (active) {
+            tc_ld32(taddr + c * 32, r);
+            tc_ld_wait();
+          }
+          if (c == 3) {  // accumulator fully read: hand the buffer back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctl.tempty[ab]));
+          }
+          if (!active) continue;
+          if (BLOCK) {
+            if (p.dump) {
+              int32_t* o = static_cast<int32_t*>(p.c) +
+                           (((int64_t)batch * KB + d) * p.M + (row - (int64_t)batch * p.M)) * p.N + col0 + c * 32;
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+            } else if (fast_scalar) {
+              const float f = sa * sb;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(__int2float_rn((int)r[j]), f, acc[c * 32 + j]);
+            } else {
+              const float* sbv = p.b_kind == I8L_BSCALE_CHANNEL ? ctl.bscale[wg]
+                                 : p.b_kind == I8L_BSCALE_GROUP ? ctl.bstep[wg][d & 1]
+                                                                : nullptr;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float pf = __int2float_rn((int)r[j]);
+                const float sbj = sbv ? sbv[c * 32 + j] : sb;
+                float term;
+                if (p.divide) term = __fdiv_rn(pf, __fmul_rn(sa, sbj));
+                else term = __fmul_rn(__fmul_rn(pf, sa), sbj);
+                acc[c * 32 + j] = __fadd_rn(acc[c * 32 + j], term);
+              }
+            }
+          } else {
+            // row x column epilogue straight from the accumulator chunk
+            if (p.dump) {
+              int32_t* o = static_cast<int32_t*>(p.c) + row * p.N + col0 + c * 32;
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+            } else {
+              const float sar = __ldg(p.a_scale + row);
+              float v[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                v[j] = __fmul_rn(__fmul_rn(__int2float_rn((int)r[j]), sar), ctl.bscale[wg][c * 32 + j]);
+                if (!p.out_f32 && (p.post_scale != 1.f || p.bias)) {
+                  v[j] = round_to_bf16(v[j]);  // the reference rounds to bf16 before its 1/K pass
+                  v[j] = __fmul_rn(v[j], p.post_scale);
+                  if (p.bias) v[j] = __fadd_rn(v[j], __bfloat162float(p.bias[col0 + c * 32 + j]));
+                }
+              }
+              if (p.out_f32) {
+                float* o = static_cast<float*>(p.c) + row * p.N + col0 + c * 32;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                  *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              } else {
+                __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.c) + row * p.N + col0 + c * 32;
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                  __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                  uint4 u;
+                  u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
+                  u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
+                  *reinterpret_cast<uint4*>(o + j) = u;
+                }
+              }
+            }
+          }
+        }
+        ab ^= 1;
+        if (ab == 0) aph ^= 1u;
+      }
+      if (BLOCK && ok && active && !p.dump) {
+        const bool b_at_end = fast_scalar && p.b_kind == I8L_BSCALE_CHANNEL;
+#pragma unroll
+        for (int j0 = 0; j0 < 128; j0 += 8) {
+          float v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            v[j] = acc[j0 + j];
+            if (b_at_end) v[j] *= ctl.bscale[wg][j0 + j];
+            if (p.post_scale != 1.f) v[j] = __fmul_rn(v[j], p.post_scale);
+            if (p.bias) v[j] = __fadd_rn(v[j], __bfloat162float(p.bias[col0 + j0 + j]));
+          }
+          if (p.out_f32) {
+            float* o = static_cast<float*>(p.c) + row * p.N + col0 + j0;
+            *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+          } else {
+            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.c) + row * p.N + col0 + j0;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]), h3 = __floats2bfloat162_rn(v[6], v[7]);
+            uint4 u;
+            u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
+            u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(o) = u;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && ctl.abort_flag && p.status) atomicExch(p.status, I8L_ERR_TIMEOUT);
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// int8 [rows, K] row-major -> boxes of box_rows x 128 bytes, 128B swizzle.
+static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return fail(I8L_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t gstr[1] = {(cuuint64_t)K};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), gdim, gstr, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(I8L_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return I8L_OK;
+}
+
+static int sm_count() {
+  static int cached[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
+  return cached[dev];
+}
+
+static int launch_gemm(bool block, const int8_t* a_q, const int8_t* b_q, GemmParams p, int64_t batch, int64_t M,
+                       int64_t N, int64_t K, cudaStream_t st) {
+  if (batch <= 0 || M <= 0 || N <= 0 || K <= 0 || M % 128 || N % 128 || K % 128)
+    return fail(I8L_ERR_SHAPE, "batch=%lld M=%lld N=%lld K=%lld: all positive, M, N, K multiples of 128",
+                (long long)batch, (long long)M, (long long)N, (long long)K);
+  if (batch * M >= (1ll << 31) || batch * N >= (1ll << 31) || K >= (1ll << 31) ||
+      (batch * M / 128) * ((N + BN - 1) / BN) >= (1ll << 31))
+    return fail(I8L_ERR_SHAPE, "problem too large for 32-bit tile coordinates");
+  if (!a_q || !b_q || !p.c) return fail(I8L_ERR_ARG, "null pointer");
+  if (!aligned16(a_q) || !aligned16(b_q) || !aligned16(p.c)) return fail(I8L_ERR_ALIGN, "a_q, b_q, c must be 16-byte aligned");
+  if (int e = check_arch()) return e;
+  CUtensorMap ma, mb;
+  if (int e = make_map(&ma, a_q, batch * M, K, BM)) return e;
+  if (int e = make_map(&mb, b_q, p.b_batched ? batch * N : N, K, BN)) return e;
+  p.m_blocks = (int)(batch * M / 128);
+  p.mpb = (int)(M / 128);
+  p.n_tiles = (int)((N + BN - 1) / BN);
+  p.M = (int)M;
+  p.N = (int)N;
+  p.KB = (int)(K / 128);
+  p.raster = 16;
+  const int64_t tiles = (int64_t)p.m_blocks * p.n_tiles;
+  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  if (block) {
+    I8L_CUDA_OK(cudaFuncSetAttribute(gemm_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
+    gemm_i8_kernel<true><<<grid, THREADS, SMEM_DYN, st>>>(ma, mb, p);
+  } else {
+    I8L_CUDA_OK(cudaFuncSetAttribute(gemm_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
+    gemm_i8_kernel<false><<<grid, THREADS, SMEM_DYN, st>>>(ma, mb, p);
+  }
+  I8L_CUDA_OK(cudaGetLastError());
+  return I8L_OK;
+}
+
+}  // namespace i8l
+
+using namespace i8l;
+
+extern "C" int i8l_gemm_block(const int8_t* a_q, const int8_t* b_q, const float* a_scale, const float* b_scale,
+                              int a_scale_kind, int b_scale_kind, int b_batched, const void* bias, float post_scale,
+                              void* c, int64_t batch, int64_t M, int64_t N, int64_t K, int flags, int32_t* status,
+                              void* stream) {
+  if (!a_scale || !b_scale) return fail(I8L_ERR_ARG, "null scale pointer");
+  if (a_scale_kind != I8L_ASCALE_TILE && a_scale_kind != I8L_ASCALE_GROUP) return fail(I8L_ERR_ARG, "bad a_scale_kind");
+  if (b_scale_kind < I8L_BSCALE_CHANNEL || b_scale_kind > I8L_BSCALE_GROUP) return fail(I8L_ERR_ARG, "bad b_scale_kind");
+  if ((flags & I8L_GEMM_DIVIDE) && b_scale_kind == I8L_BSCALE_CHANNEL)
+    return fail(I8L_ERR_ARG, "I8L_GEMM_DIVIDE needs per-K-block b scales");
+  GemmParams p{};
+  p.a_scale = a_scale; p.b_scale = b_scale; p.bias = static_cast<const __nv_bfloat16*>(bias); p.c = c;
+  p.status = status; p.a_kind = a_scale_kind; p.b_kind = b_scale_kind; p.b_batched = b_batched ? 1 : 0;
+  p.exact = (flags & (I8L_GEMM_EXACT_ORDER | I8L_GEMM_DIVIDE)) ? 1 : 0;
+  p.divide = (flags & I8L_GEMM_DIVIDE) ? 1 : 0;
+  p.out_f32 = (flags & I8L_GEMM_OUT_F32) ? 1 : 0;
+  p.post_scale = post_scale;
+  return launch_gemm(true, a_q, b_q, p, batch, M, N, K, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int i8l_gemm_rowcol(const int8_t* a_q, const int8_t* b_q, const float* a_scale, const float* b_scale,
+                               int b_batched, const void* bias, float post_scale, void* c, int64_t batch, int64_t M,
+                               int64_t N, int64_t K, int flags, int32_t* status, void* stream) {
+  if (!a_scale || !b_scale) return fail(I8L_ERR_ARG, "null scale pointer");
+  GemmParams p{};
+  p.a_scale = a_scale; p.b_scale = b_scale; p.bias = static_cast<const __nv_bfloat16*>(bias); p.c = c;
+  p.status = status; p.b_batched = b_batched ? 1 : 0; p.b_kind = I8L_BSCALE_CHANNEL;
+  p.out_f32 = (flags & I8L_GEMM_OUT_F32) ? 1 : 0;
+  p.post_scale = post_scale;
+  return launch_gemm(false, a_q, b_q, p, batch, M, N, K, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int i8l_gemm_dump_i32(const int8_t* a_q, const int8_t* b_q, int b_batched, int32_t* out, int64_t batch,
+                                 int64_t M, int64_t N, int64_t K, int per_block, int32_t* status, void* stream) {
+  GemmParams p{};
+  p.c = out; p.status = status; p.b_batched = b_batched ? 1 : 0; p.dump = per_block ? 2 : 1; p.post_scale = 1.f;
+  return launch_gemm(per_block != 0, a_q, b_q, p, batch, M, N, K, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,496 @@
+// bf16 -> int8 absmax quantizers (HBM-bound): 128x128-tile kernel with optional transposed
+// output and fused 128-point Hadamard rotation, whole-row kernel, column-absmax kernel.
+#include <cstdarg>
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace i8l {
+
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_arch() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return fail(I8L_ERR_CUDA, "cudaGetDevice failed");
+  static int cached_major[64];  // 0 = unknown
+  int major = (dev >= 0 && dev < 64) ? cached_major[dev] : 0;
+  if (major == 0) {
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
+      return fail(I8L_ERR_CUDA, "cudaDeviceGetAttribute failed");
+    if (dev >= 0 && dev < 64) cached_major[dev] = major;
+  }
+  if (major != 10)
+    return fail(I8L_ERR_ARCH, "device %d has compute capability %d.x; this library is sm_100a only", dev, major);
+  return I8L_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Tile kernel.  One CTA of 256 threads owns one 128x128 tile of x.
+// Thread mapping: warp w owns tile rows 16w..16w+15; pass it in {0,1}; lane = (half<<4)|cc;
+// the thread holds rows 16w + 8it + 4half + i (i<4), columns 8cc..8cc+7: every global load is a
+// 16-byte vector and 16 lanes cover one 256-byte row segment.
+// ------------------------------------------------------------------------------------------------
+constexpr int GRAN_COLFULL = 3;  // internal: per-column scale from a precomputed column absmax
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+  return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) |
+         ((uint32_t)(d & 0xff) << 24);
+}
+
+template <int GRAN, int MODE, bool HAD, bool OUT_N, bool OUT_T>
+__global__ void __launch_bounds__(256)
+quant_tile_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t cols,
+                  int8_t* __restrict__ q, float* __restrict__ scale, int8_t* __restrict__ qt,
+                  float* __restrict__ scale_t, const float* __restrict__ colmax) {
+  __shared__ float s_red[8];
+  __shared__ float s_colred[(GRAN == I8L_GRAN_GROUP128 && OUT_T) ? 8 * 128 : 1];
+  __shared__ float s_cols[(GRAN != I8L_GRAN_TILE128 && OUT_T) ? 128 : 1];
+  __shared__ uint32_t s_t[OUT_T ? 128 * 32 : 1];
+
+  const int tid = threadIdx.x, w = tid >> 5, l = tid & 31, cc = l & 15, half = l >> 4;
+  const int64_t r_base = (int64_t)blockIdx.y * 128, c_base = (int64_t)blockIdx.x * 128;
+  const int64_t boff = (int64_t)blockIdx.z * rows * cols;
+  const __nv_bfloat16* xb = x + boff;
+
+  float v[2][4][8];
+#pragma unroll
+  for (int it = 0; it < 2; ++it)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = 16 * w + 8 * it + 4 * half + i;
+      const uint4 u = __ldg(reinterpret_cast<const uint4*>(xb + (r_base + r) * cols + c_base + 8 * cc));
+      unpack8(u, v[it][i]);
+      if (HAD) {
+        fwht128_lanes16(v[it][i], l);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[it][i][j] = round_to_bf16(v[it][i][j]);
+      }
+    }
+
+  // ---- scales
+  float s_tile = 0.f;          // TILE128
+  float s_row[2][4];           // GROUP128 natural
+  float s_col[8];              // column scales (GROUP128 transposed / COLFULL)
+  if (GRAN == I8L_GRAN_TILE128) {
+    float m = 0.f;
+#pragma unroll
+    for (int it = 0; it < 2; ++it)
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(v[it][i][j]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (l == 0) s_red[w] = m;
+    __syncthreads();
+    m = s_red[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) m = fmaxf(m, s_red[k]);
+    float stored;
+    make_scale<MODE>(m, s_tile, stored);
+    if (tid == 0) {
+      const int64_t nrb = rows / 128, ncb = cols / 128;
+      if (OUT_N) scale[((int64_t)blockIdx.z * nrb + blockIdx.y) * ncb + blockIdx.x] = stored;
+      if (OUT_T) scale_t[((int64_t)blockIdx.z * ncb + blockIdx.x) * nrb + blockIdx.y] = stored;
+    }
+  } else if (GRAN == I8L_GRAN_GROUP128 && OUT_N) {
+#pragma unroll
+    for (int it = 0; it < 2; ++it)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float m = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(v[it][i][j]));
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float stored;
+        make_scale<MODE>(m, s_row[it][i], stored);
+        if (cc == 0) {
+          const int r = 16 * w + 8 * it + 4 * half + i;
+          scale[((int64_t)blockIdx.z * rows + r_base + r) * (cols / 128) + blockIdx.x] = stored;
+        }
+      }
+  } else {  // column scales
+    if (GRAN == I8L_GRAN_GROUP128) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float m = 0.f;
+#pragma unroll
+        for (int it = 0; it < 2; ++it)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) m = fmaxf(m, fabsf(v[it][i][j]));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+        if (half == 0) s_colred[w * 128 + 8 * cc + j] = m;
+      }
+      __syncthreads();
+    }
+    if (tid < 128) {
+      float m;
+      if (GRAN == I8L_GRAN_GROUP128) {
+        m = s_colred[tid];
+#pragma unroll
+        for (int k = 1; k < 8; ++k) m = fmaxf(m, s_colred[k * 128 + tid]);
+      } else {
+        m = colmax[c_base + tid];
+      }
+      float s, stored;
+      make_scale<MODE>(m, s, stored);
+      s_cols[tid] = s;
+      if (GRAN == I8L_GRAN_GROUP128)
+        scale_t[((int64_t)blockIdx.z * cols + c_base + tid) * (rows / 128) + blockIdx.y] = stored;
+      else if (blockIdx.y == 0)
+        scale_t[c_base + tid] = stored;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s_col[j] = s_cols[8 * cc + j];
+  }
+
+  // ---- quantise, write
+#pragma unroll
+  for (int it = 0; it < 2; ++it) {
+    int b[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float s;
+        if (GRAN == I8L_GRAN_TILE128) s = s_tile;
+        else if (GRAN == I8L_GRAN_GROUP128 && OUT_N) s = s_row[it][i];
+        else s = s_col[j];
+        b[i][j] = quant1<MODE>(v[it][i][j], s);
+      }
+    if (OUT_N) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = 16 * w + 8 * it + 4 * half + i;
+        uint2 o;
+        o.x = pack4(b[i][0], b[i][1], b[i][2], b[i][3]);
+        o.y = pack4(b[i][4], b[i][5], b[i][6], b[i][7]);
+        *reinterpret_cast<uint2*>(q + boff + (r_base + r) * cols + c_base + 8 * cc) = o;
+      }
+    }
+    if (OUT_T) {
+      // word (4 consecutive rows of one column) goes to transposed row c = 8cc+j, word index
+      // widx = 4w + 2it + half, XOR-swizzled with 2*(c>>3) so that the 32 lanes hit 32 banks.
+      const int widx = 4 * w + 2 * it + half;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int c = 8 * cc + j;
+        s_t[c * 32 + (widx ^ (2 * cc))] = pack4(b[0][j], b[1][j], b[2][j], b[3][j]);
+      }
+    }
+  }
+  if (OUT_T) {
+    __syncthreads();
+    int8_t* qtb = qt + boff;
+#pragma unroll 4
+    for (int t = 0; t < 16; ++t) {
+      const int c = 16 * w + t;
+      const uint32_t word = s_t[c * 32 + (l ^ (2 * (c >> 3)))];
+      *reinterpret_cast<uint32_t*>(qtb + (c_base + c) * rows + r_base + 4 * l) = word;
+    }
+  }
+}
+
+// Column absmax of x [rows, cols] into colmax[cols] (pre-zeroed); |x| >= 0 so the float bit
+// patterns order like integers and atomicMax on int is exact.
+__global__ void __launch_bounds__(256)
+col_absmax_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t cols, float* __restrict__ colmax) {
+  __shared__ float s_colred[8 * 128];
+  const int tid = threadIdx.x, w = tid >> 5, l = tid & 31, cc = l & 15, half = l >> 4;
+  const int64_t r_base = (int64_t)blockIdx.y * 128, c_base = (int64_t)blockIdx.x * 128;
+  float m[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) m[j] = 0.f;
+#pragma unroll
+  for (int it = 0; it < 2; ++it)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = 16 * w + 8 * it + 4 * half + i;
+      const uint4 u = __ldg(reinterpret_cast<const uint4*>(x + (r_base + r) * cols + c_base + 8 * cc));
+      float v[8];
+      unpack8(u, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m[j] = fmaxf(m[j], fabsf(v[j]));
+    }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    m[j] = fmaxf(m[j], __shfl_xor_sync(0xffffffffu, m[j], 16));
+    if (half == 0) s_colred[w * 128 + 8 * cc + j] = m[j];
+  }
+  __syncthreads();
+  if (tid < 128) {
+    float mm = s_colred[tid];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) mm = fmaxf(mm, s_colred[k * 128 + tid]);
+    atomicMax(reinterpret_cast<int*>(colmax + c_base + tid), __float_as_int(mm));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Row kernel: one CTA per row, two sweeps over the row (the second one hits L1/L2).
+// HAD128: the 16 lanes that hold one 128-wide group rotate it with shuffles in both sweeps.
+// ------------------------------------------------------------------------------------------------
+template <int MODE, bool HAD128>
+__global__ void __launch_bounds__(256)
+quant_row_kernel(const __nv_bfloat16* __restrict__ x, int64_t cols, int8_t* __restrict__ q,
+                 float* __restrict__ scale) {
+  __shared__ float s_red[8];
+  const int tid = threadIdx.x, l = tid & 31;
+  const int64_t row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * cols);
+  const int nchunks = (int)(cols / 8);
+
+  float m = 0.f;
+  for (int base = 0; base < nchunks; base += 256) {
+    const int ch = base + tid;
+    float v[8];
+    if (ch < nchunks) unpack8(__ldg(xr + ch), v);
+    else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    }
+    if (HAD128) {
+      fwht128_lanes16(v, l);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = round_to_bf16(v[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(v[j]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (l == 0) s_red[tid >> 5] = m;
+  __syncthreads();
+  m = s_red[0];
+#pragma unroll
+  for (int k = 1; k < 8; ++k) m = fmaxf(m, s_red[k]);
+  float s, stored;
+  make_scale<MODE>(m, s, stored);
+  if (tid == 0) scale[row] = stored;
+
+  uint2* qr = reinterpret_cast<uint2*>(q + row * cols);
+  for (int base = 0; base < nchunks; base += 256) {
+    const int ch = base + tid;
+    float v[8];
+    if (ch < nchunks) unpack8(__ldg(xr + ch), v);
+    else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    }
+    if (HAD128) {
+      fwht128_lanes16(v, l);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = round_to_bf16(v[j]);
+    }
+    if (ch < nchunks) {
+      uint2 o;
+      o.x = pack4(quant1<MODE>(v[0], s), quant1<MODE>(v[1], s), quant1<MODE>(v[2], s), quant1<MODE>(v[3], s));
+      o.y = pack4(quant1<MODE>(v[4], s), quant1<MODE>(v[5], s), quant1<MODE>(v[6], s), quant1<MODE>(v[7], s));
+      qr[ch] = o;
+    }
+  }
+}
+
+// Whole-row Hadamard (power-of-two cols <= 32768): the row lives in shared memory as fp32.
+// Spans 1..64 run in registers/shuffles exactly as above, spans >= 128 as shared-memory passes.
+template <int MODE>
+__global__ void __launch_bounds__(256)
+quant_row_hadfull_kernel(const __nv_bfloat16* __restrict__ x, int64_t cols, int8_t* __restrict__ q,
+                         float* __restrict__ scale) {
+  extern __shared__ float s_row[];
+  __shared__ float s_red[8];
+  const int tid = threadIdx.x, l = tid & 31;
+  const int64_t row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * cols);
+  const int n = (int)cols, nchunks = n / 8;
+
+  for (int base = 0; base < nchunks; base += 256) {
+    const int ch = base + tid;
+    float v[8];
+    if (ch < nchunks) unpack8(__ldg(xr + ch), v);
+    else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    }
+    fwht128_lanes16(v, l);
+    if (ch < nchunks) {
+      *reinterpret_cast<float4*>(s_row + 8 * ch) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(s_row + 8 * ch + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+  }
+  __syncthreads();
+  for (int h = 128; h < n; h <<= 1) {
+    for (int p = tid; p < n / 2; p += 256) {
+      const int i = ((p & ~(h - 1)) << 1) | (p & (h - 1));
+      const float a = s_row[i], b = s_row[i + h];
+      s_row[i] = __fadd_rn(a, b);
+      s_row[i + h] = __fsub_rn(a, b);
+    }
+    __syncthreads();
+  }
+  float m = 0.f;
+  for (int i = tid; i < n; i += 256) {
+    const float r = round_to_bf16(s_row[i]);
+    s_row[i] = r;
+    m = fmaxf(m, fabsf(r));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (l == 0) s_red[tid >> 5] = m;
+  __syncthreads();
+  m = s_red[0];
+#pragma unroll
+  for (int k = 1; k < 8; ++k) m = fmaxf(m, s_red[k]);
+  float s, stored;
+  make_scale<MODE>(m, s, stored);
+  if (tid == 0) scale[row] = stored;
+  uint32_t* qr = reinterpret_cast<uint32_t*>(q + row * cols);
+  for (int i = tid; i < n / 4; i += 256) {
+    const float4 f = *reinterpret_cast<const float4*>(s_row + 4 * i);
+    qr[i] = pack4(quant1<MODE>(f.x, s), quant1<MODE>(f.y, s), quant1<MODE>(f.z, s), quant1<MODE>(f.w, s));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host
+static int check_dims(int64_t batch, int64_t rows, int64_t cols) {
+  if (batch <= 0 || rows <= 0 || cols <= 0 || rows % 128 || cols % 128)
+    return fail(I8L_ERR_SHAPE, "batch=%lld rows=%lld cols=%lld: all must be positive and rows, cols multiples of 128",
+                (long long)batch, (long long)rows, (long long)cols);
+  if (batch > 65535 || rows / 128 > 65535 || rows * cols >= (1ll << 40))
+    return fail(I8L_ERR_SHAPE, "shape too large for the launch grid");
+  return I8L_OK;
+}
+
+template <int GRAN, int MODE, bool HAD, bool OUT_N, bool OUT_T>
+static void launch_tile(const void* x, int64_t batch, int64_t rows, int64_t cols, int8_t* q, float* scale,
+                        int8_t* qt, float* scale_t, const float* colmax, cudaStream_t st) {
+  dim3 grid((unsigned)(cols / 128), (unsigned)(rows / 128), (unsigned)batch);
+  quant_tile_kernel<GRAN, MODE, HAD, OUT_N, OUT_T><<<grid, 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(x), rows, cols, q, scale, qt, scale_t, colmax);
+}
+
+template <int GRAN, int MODE>
+static int dispatch_tile(const void* x, int64_t batch, int64_t rows, int64_t cols, bool had, int8_t* q,
+                         float* scale, int8_t* qt, float* scale_t, const float* colmax, cudaStream_t st) {
+  const bool n = q != nullptr, t = qt != nullptr;
+  if (had) {
+    if (t) return fail(I8L_ERR_ARG, "Hadamard rotation with transposed output is not available in the tile kernel");
+    launch_tile<GRAN, MODE, true, true, false>(x, batch, rows, cols, q, scale, qt, scale_t, colmax, st);
+  } else if (GRAN == I8L_GRAN_TILE128) {
+    if (n && t) launch_tile<GRAN, MODE, false, true, true>(x, batch, rows, cols, q, scale, qt, scale_t, colmax, st);
+    else if (n) launch_tile<GRAN, MODE, false, true, false>(x, batch, rows, cols, q, scale, qt, scale_t, colmax, st);
+    else launch_tile<GRAN, MODE, false, false, true>(x, batch, rows, cols, q, scale, qt, scale_t, colmax, st);
+  } else {  // grouped scales differ between the two orientations: one launch each
+    if (n) launch_tile<GRAN, MODE, false, true, false>(x, batch, rows, cols, q, scale, nullptr, nullptr, colmax, st);
+    if (t) launch_tile<GRAN, MODE, false, false, true>(x, batch, rows, cols, nullptr, nullptr, qt, scale_t, colmax, st);
+  }
+  I8L_CUDA_OK(cudaGetLastError());
+  return I8L_OK;
+}
+
+}  // namespace i8l
+
+using namespace i8l;
+
+extern "C" const char* i8l_last_error(void) { return g_err; }
+extern "C" int i8l_version(void) { return 100; }
+
+extern "C" int i8l_quant_tile(const void* x, int64_t batch, int64_t rows, int64_t cols, int gran, int qmode,
+                              int hadamard, int8_t* q, float* scale, int8_t* qt, float* scale_t, void* stream) {
+  if (int e = check_dims(batch, rows, cols)) return e;
+  if (!x || (!q && !qt) || (q && !scale) || (qt && !scale_t)) return fail(I8L_ERR_ARG, "null pointer");
+  if (!aligned16(x) || !aligned16(q) || !aligned16(qt)) return fail(I8L_ERR_ALIGN, "x, q, qt must be 16-byte aligned");
+  if (hadamard != I8L_HAD_NONE && hadamard != I8L_HAD_128)
+    return fail(I8L_ERR_ARG, "i8l_quant_tile: hadamard must be NONE or 128");
+  if (int e = check_arch()) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool had = hadamard == I8L_HAD_128;
+#define I8L_TILE_CASE(G, Mo) \
+  if (gran == G && qmode == Mo) return dispatch_tile<G, Mo>(x, batch, rows, cols, had, q, scale, qt, scale_t, nullptr, st);
+  I8L_TILE_CASE(I8L_GRAN_TILE128, I8L_QMODE_TRITON)
+  I8L_TILE_CASE(I8L_GRAN_TILE128, I8L_QMODE_RNE)
+  I8L_TILE_CASE(I8L_GRAN_TILE128, I8L_QMODE_FUSED)
+  I8L_TILE_CASE(I8L_GRAN_GROUP128, I8L_QMODE_TRITON)
+  I8L_TILE_CASE(I8L_GRAN_GROUP128, I8L_QMODE_RNE)
+  I8L_TILE_CASE(I8L_GRAN_GROUP128, I8L_QMODE_FUSED)
+#undef I8L_TILE_CASE
+  return fail(I8L_ERR_ARG, "i8l_quant_tile: unsupported gran=%d qmode=%d", gran, qmode);
+}
+
+extern "C" int i8l_quant_row(const void* x, int64_t rows, int64_t cols, int qmode, int hadamard, int8_t* q,
+                             float* scale, void* stream) {
+  if (rows <= 0 || cols <= 0 || cols % 128 || rows > 0x7fffffffll || cols > (1 << 20))
+    return fail(I8L_ERR_SHAPE, "rows=%lld cols=%lld: need rows>0, cols a positive multiple of 128",
+                (long long)rows, (long long)cols);
+  if (!x || !q || !scale) return fail(I8L_ERR_ARG, "null pointer");
+  if (!aligned16(x) || !aligned16(q)) return fail(I8L_ERR_ALIGN, "x, q must be 16-byte aligned");
+  if (int e = check_arch()) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  if (hadamard == I8L_HAD_FULL) {
+    if ((cols & (cols - 1)) || cols > 32768)
+      return fail(I8L_ERR_SHAPE, "full Hadamard needs cols a power of two <= 32768, got %lld", (long long)cols);
+    const size_t smem = (size_t)cols * sizeof(float);
+#define I8L_HF_CASE(Mo)                                                                                        \
+  if (qmode == Mo) {                                                                                           \
+    I8L_CUDA_OK(cudaFuncSetAttribute(quant_row_hadfull_kernel<Mo>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                     (int)smem));                                                              \
+    quant_row_hadfull_kernel<Mo><<<(unsigned)rows, 256, smem, st>>>(xp, cols, q, scale);                       \
+    I8L_CUDA_OK(cudaGetLastError());                                                                           \
+    return I8L_OK;                                                                                             \
+  }
+    I8L_HF_CASE(I8L_QMODE_TRITON)
+    I8L_HF_CASE(I8L_QMODE_RNE)
+    I8L_HF_CASE(I8L_QMODE_ROWRCP)
+#undef I8L_HF_CASE
+    return fail(I8L_ERR_ARG, "i8l_quant_row: unsupported qmode=%d", qmode);
+  }
+  if (hadamard != I8L_HAD_NONE && hadamard != I8L_HAD_128) return fail(I8L_ERR_ARG, "bad hadamard=%d", hadamard);
+#define I8L_ROW_CASE(Mo)                                                                              \
+  if (qmode == Mo) {                                                                                  \
+    if (hadamard) quant_row_kernel<Mo, true><<<(unsigned)rows, 256, 0, st>>>(xp, cols, q, scale);     \
+    else quant_row_kernel<Mo, false><<<(unsigned)rows, 256, 0, st>>>(xp, cols, q, scale);             \
+    I8L_CUDA_OK(cudaGetLastError());                                                                  \
+    return I8L_OK;                                                                                    \
+  }
+  I8L_ROW_CASE(I8L_QMODE_TRITON)
+  I8L_ROW_CASE(I8L_QMODE_RNE)
+  I8L_ROW_CASE(I8L_QMODE_ROWRCP)
+#undef I8L_ROW_CASE
+  return fail(I8L_ERR_ARG, "i8l_quant_row: unsupported qmode=%d", qmode);
+}
+
+extern "C" int i8l_quant_col_t(const void* x, int64_t rows, int64_t cols, int qmode, int8_t* qt, float* scale_t,
+                               float* colmax_scratch, void* stream) {
+  if (int e = check_dims(1, rows, cols)) return e;
+  if (!x || !qt || !scale_t || !colmax_scratch) return fail(I8L_ERR_ARG, "null pointer");
+  if (!aligned16(x) || !aligned16(qt)) return fail(I8L_ERR_ALIGN, "x, qt must be 16-byte aligned");
+  if (int e = check_arch()) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  I8L_CUDA_OK(cudaMemsetAsync(colmax_scratch, 0, (size_t)cols * sizeof(float), st));
+  dim3 grid((unsigned)(cols / 128), (unsigned)(rows / 128), 1);
+  col_absmax_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows, cols, colmax_scratch);
+  I8L_CUDA_OK(cudaGetLastError());
+#define I8L_COL_CASE(Mo)                                                                                     \
+  if (qmode == Mo) {                                                                                         \
+    launch_tile<GRAN_COLFULL, Mo, false, false, true>(x, 1, rows, cols, nullptr, nullptr, qt, scale_t,       \
+                                                      colmax_scratch, st);                                   \
+    I8L_CUDA_OK(cudaGetLastError());                                                                         \
+    return I8L_OK;                                                                                           \
+  }
+  I8L_COL_CASE(I8L_QMODE_TRITON)
+  I8L_COL_CASE(I8L_QMODE_RNE)
+  I8L_COL_CASE(I8L_QMODE_ROWRCP)
+#undef I8L_COL_CASE
+  return fail(I8L_ERR_ARG, "i8l_quant_col_t: unsupported qmode=%d", qmode);
+}

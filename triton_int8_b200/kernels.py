@@ -1,0 +1,106 @@
+"""Tensor-level wrappers of the C ABI: allocate outputs with torch, pass raw pointers and the
+current CUDA stream.  These are the building blocks of the fwd_32 / bwd_33 variants."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib as L
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _check_bf16(x: torch.Tensor, name: str) -> torch.Tensor:
+    if not x.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (no CPU path exists)")
+    if x.dtype != torch.bfloat16:
+        raise TypeError(f"{name} must be bfloat16, got {x.dtype}")
+    return x.contiguous()
+
+
+def quant_tile(x: torch.Tensor, gran: int = L.GRAN_TILE128, qmode: int = L.QMODE_TRITON, hadamard: int = 0,
+               natural: bool = True, transposed: bool = False):
+    """x bf16 [B, R, C] -> (q, scale, qt, scale_t); entries not requested are None."""
+    x = _check_bf16(x, "x")
+    B, R, C = x.shape
+    q = s = qt = st = None
+    if natural:
+        q = torch.empty((B, R, C), dtype=torch.int8, device=x.device)
+        s = torch.empty((B, R // 128, C // 128) if gran == L.GRAN_TILE128 else (B, R, C // 128),
+                        dtype=torch.float32, device=x.device)
+    if transposed:
+        qt = torch.empty((B, C, R), dtype=torch.int8, device=x.device)
+        st = torch.empty((B, C // 128, R // 128) if gran == L.GRAN_TILE128 else (B, C, R // 128),
+                         dtype=torch.float32, device=x.device)
+    L.call("i8l_quant_tile", x.data_ptr(), B, R, C, gran, qmode, hadamard, _ptr(q), _ptr(s), _ptr(qt), _ptr(st),
+           _stream())
+    return q, s, qt, st
+
+
+def quant_row(x: torch.Tensor, qmode: int = L.QMODE_TRITON, hadamard: int = 0):
+    """x bf16 [..., C] -> int8 [..., C], fp32 scale [...]."""
+    x = _check_bf16(x, "x")
+    C = x.shape[-1]
+    rows = x.numel() // C
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    s = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    L.call("i8l_quant_row", x.data_ptr(), rows, C, qmode, hadamard, q.data_ptr(), s.data_ptr(), _stream())
+    return q, s
+
+
+def quant_col_t(x: torch.Tensor, qmode: int = L.QMODE_TRITON):
+    """x bf16 [R, C] -> int8 x^T [C, R] with one scale per column of x, fp32 [C]."""
+    x = _check_bf16(x, "x")
+    R, C = x.shape
+    qt = torch.empty((C, R), dtype=torch.int8, device=x.device)
+    st = torch.empty((C,), dtype=torch.float32, device=x.device)
+    scratch = torch.empty((C,), dtype=torch.float32, device=x.device)
+    L.call("i8l_quant_col_t", x.data_ptr(), R, C, qmode, qt.data_ptr(), st.data_ptr(), scratch.data_ptr(), _stream())
+    return qt, st
+
+
+def _gemm_dims(aq: torch.Tensor, bq: torch.Tensor):
+    if aq.dtype != torch.int8 or bq.dtype != torch.int8:
+        raise TypeError("quantized operands must be int8")
+    B, M, K = aq.shape
+    b_batched = bq.dim() == 3
+    N = bq.shape[-2]
+    if bq.shape[-1] != K or (b_batched and bq.shape[0] != B):
+        raise ValueError(f"operand shapes do not match: {tuple(aq.shape)} x {tuple(bq.shape)}")
+    return B, M, N, K, b_batched
+
+
+def gemm_block(aq, bq, a_s, b_s, a_kind=L.ASCALE_TILE, b_kind=L.BSCALE_CHANNEL, bias=None, post_scale=1.0,
+               flags=0, status=None):
+    """Block-scaled GEMM; returns bf16 (fp32 with GEMM_OUT_F32) [B, M, N]."""
+    aq, bq = aq.contiguous(), bq.contiguous()
+    B, M, N, K, bb = _gemm_dims(aq, bq)
+    out = torch.empty((B, M, N), dtype=torch.float32 if flags & L.GEMM_OUT_F32 else torch.bfloat16, device=aq.device)
+    L.call("i8l_gemm_block", aq.data_ptr(), bq.data_ptr(), a_s.contiguous().data_ptr(), b_s.contiguous().data_ptr(),
+           a_kind, b_kind, int(bb), _ptr(bias), float(post_scale), out.data_ptr(), B, M, N, K, flags, _ptr(status),
+           _stream())
+    return out
+
+
+def gemm_rowcol(aq, bq, a_s, b_s, bias=None, post_scale=1.0, flags=0, status=None):
+    aq, bq = aq.contiguous(), bq.contiguous()
+    B, M, N, K, bb = _gemm_dims(aq, bq)
+    out = torch.empty((B, M, N), dtype=torch.float32 if flags & L.GEMM_OUT_F32 else torch.bfloat16, device=aq.device)
+    L.call("i8l_gemm_rowcol", aq.data_ptr(), bq.data_ptr(), a_s.contiguous().data_ptr(), b_s.contiguous().data_ptr(),
+           int(bb), _ptr(bias), float(post_scale), out.data_ptr(), B, M, N, K, flags, _ptr(status), _stream())
+    return out
+
+
+def gemm_dump_i32(aq, bq, per_block=False, status=None):
+    aq, bq = aq.contiguous(), bq.contiguous()
+    B, M, N, K, bb = _gemm_dims(aq, bq)
+    shape = (B, K // 128, M, N) if per_block else (B, M, N)
+    out = torch.empty(shape, dtype=torch.int32, device=aq.device)
+    L.call("i8l_gemm_dump_i32", aq.data_ptr(), bq.data_ptr(), int(bb), out.data_ptr(), B, M, N, K, int(per_block),
+           _ptr(status), _stream())
+    return out
