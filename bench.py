@@ -1,0 +1,385 @@
+#!/usr/bin/env python
+"""Benchmark of the INT8 quantized-linear hot path (forward + dX + dW of one linear layer).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c5|c4|c3|c2|sq8192]
+
+Workload (default c5): the Llama-70B MLP shape M=32768 tokens, K=8192, N=28672, block_channel
+scaling, W column-sharded along N over the N GPUs (strong scaling); synthetic seeded data with the
+distributions BASELINE.json names.  One step = quantize X/W, Y GEMM, quantize dY/W^T, dX GEMM
+(+ reduce-scatter when sharded), dW GEMM.  Prints ONE JSON line on rank 0.
+
+`--impl reference` times the CPU restatement of the reference semantics (oracle/) on the host
+cores over a bounded sample of the same workload; it is the only place the product bench executes
+oracle code besides the `cpu_baseline` leg.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (M, K, N, description)
+    "c5": (32768, 8192, 28672, "llama70b-mlp M=32768 K=8192 N=28672 block_channel fwd+dX+dW, W sharded along N"),
+    "c3": (16384, 4096, 11008, "llama2-7b up-proj M=16384 K=4096 N=11008 block_channel fwd+dX+dW"),
+    "sq8192": (8192, 8192, 8192, "square 8192^3 block_channel fwd+dX+dW"),
+    "c1": (512, 1024, 1024, "config-1 512x1024x1024 block_channel fwd+dX+dW"),
+}
+NOMINAL_INT8_TOPS = 4500.0  # B200 dense INT8 datasheet figure
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f), "measured"
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def make_inputs(M, K, N_local, rank, device, seed=20260004):
+    """X ~ N(0,1) with 0.5% outlier channels x30 (same on every rank), W shard ~ N(0,0.02),
+    dY shard ~ N(0,1e-3)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    x = torch.randn(M, K, generator=g, device=device, dtype=torch.float32)
+    n_out = -(-K * 5 // 1000)
+    cols = torch.randperm(K, generator=g, device=device)[:n_out]
+    x[:, cols] *= 30.0
+    x = x.to(torch.bfloat16)
+    gw = torch.Generator(device=device).manual_seed(seed + 1 + rank)
+    w = (torch.randn(N_local, K, generator=gw, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    dy = torch.empty(M, N_local, device=device, dtype=torch.bfloat16)
+    chunk = 4096
+    for r in range(0, M, chunk):  # chunked to keep the fp32 temporary small
+        dy[r:r + chunk] = (torch.randn(min(chunk, M - r), N_local, generator=gw, device=device) * 1e-3).to(torch.bfloat16)
+    return x, w, dy
+
+
+class ClockSampler:
+    """nvidia-smi sampling (read-only) during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.lines, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=lambda: [self.lines.append(l) for l in self.proc.stdout], daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for l in self.lines:
+            f = [t.strip() for t in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        busy = sorted(sm)[len(sm) // 2:]  # upper half = samples under load
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+class CpuReference:
+    """CPU restatement of the reference path (oracle/) on a bounded sample, all host threads.
+
+    Weight-only work (quantising W per output channel and W^T per input channel) is timed once on
+    the full W; token-dependent work (quantise X and dY, the Y, dX and dW GEMMs with their rescale)
+    is timed on the first `sample` tokens.  Whole-workload throughput is extrapolated linearly in the
+    token count:  tokens/s = M / (t_weight + t_tokens * M / sample)."""
+
+    def __init__(self, M, K, N, sample):
+        from oracle import ref_semantics as R
+        self.R, self.M, self.K, self.N, self.Ms = R, M, K, N, sample
+        self.cores = os.cpu_count() or 1
+        torch.set_num_threads(self.cores)
+        g = torch.Generator().manual_seed(20260004)
+        x = torch.randn(sample, K, generator=g)
+        cols = torch.randperm(K, generator=g)[: -(-K * 5 // 1000)]
+        x[:, cols] *= 30.0
+        self.x = x.to(torch.bfloat16)
+        self.w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+        self.dy = (torch.randn(sample, N, generator=g) * 1e-3).to(torch.bfloat16)
+        t0 = time.perf_counter()
+        self.wq, self.ws = R.quant_token(self.w)
+        self.wtq, self.wts = R.quant_token(self.w.t().contiguous())
+        self.t_weight = time.perf_counter() - t0
+
+    def tokens_step(self):
+        R = self.R
+        t0 = time.perf_counter()
+        xq, xs = R.quant_tile128(self.x[None])
+        y = R.gemm_block_fwd(xq, self.wq, xs, self.ws).to(torch.bfloat16)
+        dyq, dys = R.quant_tile128(self.dy[None])
+        dx = R.gemm_block_fwd(dyq, self.wtq, dys, self.wts).to(torch.bfloat16)
+        dytq, dyts = R.quant_tile128(self.dy.t().contiguous()[None], clamp=False)
+        xtq, xts = R.quant_tile128(self.x.t().contiguous()[None], clamp=False)
+        dw = R.gemm_block_bwd(dytq, xtq, dyts, xts).to(torch.bfloat16)
+        del y, dx, dw
+        return time.perf_counter() - t0
+
+    def tokens_per_s(self, t_tokens):
+        return self.M / (self.t_weight + t_tokens * self.M / self.Ms)
+
+    def describe(self, n):
+        return (f"tokens part: first {self.Ms} of {self.M} tokens (median of {n}), weight part: full W "
+                f"[{self.N},{self.K}] once; extrapolated linearly in tokens")
+
+
+def run_reference_arm(args, M, K, N, desc):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    ref = CpuReference(M, K, N, min(M, 512))
+    for _ in range(min(args.warmup, 1)):
+        ref.tokens_step()
+    n = max(1, min(args.steps, 5))
+    t_tok = statistics.median([ref.tokens_step() for _ in range(n)])
+    v = ref.tokens_per_s(t_tok)
+    print(json.dumps({
+        "impl": "reference", "metric": "linear_fwd_bwd_tokens_per_s", "value": v, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * M / v,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": desc, "timing": "host perf_counter; torch CPU int8 matmul; see cpu_baseline.sample"},
+        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": ref.cores, "kind": "port", "sample": ref.describe(n),
+                         "t_weight_s": ref.t_weight, "t_tokens_s": t_tok},
+        "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    M, K, N, desc = WORKLOADS[args.workload]
+
+    if args.impl == "reference":
+        run_reference_arm(args, M, K, N, desc)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path (use --impl reference for the CPU baseline)")
+
+    import torch.distributed as dist
+    from triton_int8_b200 import kernels as Kn, _lib as L, tp
+    from triton_int8_b200.linear import DEFAULT, grad_input, grad_weight, linear_forward, quantize_grad_output
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    L.load()
+    lo, hi = tp.shard_bounds(N, world, rank)
+    Nl = hi - lo
+    x, w, dy = make_inputs(M, K, Nl, rank, dev)
+    step_obj = tp.ColumnParallelStep(None if world == 1 else dist.group.WORLD, DEFAULT)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+    gemm_events = []
+
+    def step(record=False):
+        # forward
+        xq, xs, xqt, xst = Kn.quant_tile(x[None], L.GRAN_TILE128, L.QMODE_TRITON, 0, natural=True, transposed=True)
+        wq, ws = Kn.quant_row(w, L.QMODE_TRITON, 0)
+        e = [ev() for _ in range(6)] if record else None
+        if record: e[0].record()
+        y = Kn.gemm_block(xq, wq, xs, ws, L.ASCALE_TILE, L.BSCALE_CHANNEL)
+        if record: e[1].record()
+        # backward
+        dy_op, dyt_op = quantize_grad_output(dy, DEFAULT, True, True)
+        wtq, wts = Kn.quant_col_t(w, L.QMODE_TRITON)
+        if record: e[2].record()
+        dx_partial = Kn.gemm_block(dy_op[0], wtq, dy_op[1], wts, L.ASCALE_TILE, L.BSCALE_CHANNEL)[0]
+        if record: e[3].record()
+        if world > 1:
+            main = torch.cuda.current_stream()
+            step_obj.comm_stream.wait_stream(main)
+            with torch.cuda.stream(step_obj.comm_stream):
+                dx = tp.reduce_scatter_rows(dx_partial)
+                dx_partial.record_stream(step_obj.comm_stream)
+        else:
+            dx = dx_partial
+        if record: e[4].record()
+        dw = grad_weight(dyt_op, (xqt, xst), DEFAULT)
+        if record: e[5].record()
+        if world > 1:
+            torch.cuda.current_stream().wait_stream(step_obj.comm_stream)
+        if record:
+            gemm_events.append(e)
+        return y, dx, dw
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sync_all()
+    t0, t1 = ev(), ev()
+    with ClockSampler(local_rank) as clk:
+        time.sleep(0.25)
+        t0.record()
+        for _ in range(args.steps):
+            out = step(record=True)
+        t1.record()
+        sync_all()
+        time.sleep(0.15)
+    ms = t0.elapsed_time(t1)
+    if world > 1:
+        tms = torch.tensor([ms], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = tms.item()
+    ms_per_step = ms / args.steps
+    tokens_per_s = M / (ms_per_step * 1e-3)
+    del out
+
+    # per-GEMM device times inside the timed region (same stream as the launches)
+    def avg(i, j):
+        return statistics.mean(e[i].elapsed_time(e[j]) for e in gemm_events)
+    t_fwd, t_dx, t_dw = avg(0, 1), avg(2, 3), avg(4, 5)
+    ops = 2.0 * M * Nl * K
+    tops = {"fwd": ops / t_fwd / 1e9, "dx": ops / t_dx / 1e9, "dw": ops / t_dw / 1e9}
+    peaks, peak_src = measured_peaks()
+    int8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    t_gemm = (t_fwd + t_dx + t_dw) / 3
+    traffic = None
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+            tr = json.load(f)["gemm_i8_kernel_block"]
+            traffic = tr["dram_bytes_per_op"] * ops
+    except Exception:
+        pass
+    roofline = {
+        "bound": "tensor", "kernel": "gemm_i8_kernel<block-scaled> (avg of Y, dX, dW launches)",
+        "achieved": ops / t_gemm / 1e9, "peak": int8_peak, "unit": "TOP/s",
+        "frac": ops / t_gemm / 1e9 / int8_peak, "traffic": traffic,
+        "peak_source": f"2 x bf16_tflops_sustained of {peak_src} (no INT8 entry in MEASURED_PEAKS.json)",
+        "frac_of_nominal_4500": ops / t_gemm / 1e9 / NOMINAL_INT8_TOPS,
+        "algorithmic_ops_per_launch": ops,
+    }
+
+    # quantizer bandwidth (HBM-bound kernels), timed alone
+    def time_fn(fn, n=5):
+        fn(); torch.cuda.synchronize()
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record(); torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+    tq = time_fn(lambda: Kn.quant_tile(dy[None], L.GRAN_TILE128, L.QMODE_TRITON, 0, natural=True, transposed=True))
+    tq1 = time_fn(lambda: Kn.quant_tile(dy[None], L.GRAN_TILE128, L.QMODE_TRITON, 0, natural=True, transposed=False))
+    tr_ = time_fn(lambda: Kn.quant_row(w, L.QMODE_TRITON, 0))
+    E = dy.numel()
+    quant = {
+        "tile128_dual_out_gbs": (2 * E + 2 * E) / tq / 1e6, "tile128_gbs": (2 * E + E) / tq1 / 1e6,
+        "row_gbs": 3 * w.numel() / tr_ / 1e6, "hbm_peak_gbs": peaks["hbm_gbs"],
+        "tile128_frac": (3 * E) / tq1 / 1e6 / peaks["hbm_gbs"],
+    }
+
+    # end-to-end: host buffers in, results checksum out, through the public module API
+    e2e = None
+    if not args.no_e2e:
+        from triton_int8_b200.linear import Int8Linear
+        xh = x.cpu().pin_memory()
+        dyh = dy.cpu().pin_memory()
+        lin = Int8Linear(K, Nl, bias=False, device=dev)
+        with torch.no_grad():
+            lin.weight.copy_(w)
+        res_h = torch.empty(3, dtype=torch.float32).pin_memory()
+
+        def e2e_step():
+            xd = xh.to(dev, non_blocking=True).requires_grad_(True)
+            dyd = dyh.to(dev, non_blocking=True)
+            yy = lin(xd)
+            yy.backward(dyd)
+            dxp = xd.grad
+            if world > 1:
+                dxp = tp.reduce_scatter_rows(dxp)
+            r = torch.stack([yy[0, :128].float().sum(), dxp[0, :128].float().sum(), lin.weight.grad[0, :128].float().sum()])
+            res_h.copy_(r, non_blocking=True)
+            lin.weight.grad = None
+        n_e2e = max(2, min(args.steps, 5))
+        e2e_step(); sync_all()
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        b.record(); sync_all()
+        ems = a.elapsed_time(b)
+        if world > 1:
+            tms = torch.tensor([ems], device=dev)
+            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+            ems = tms.item()
+        e2e = {"value": M / (ems / n_e2e * 1e-3), "unit": "tokens/s",
+               "h2d_bytes_per_step": xh.numel() * 2 + dyh.numel() * 2, "d2h_bytes_per_step": 12,
+               "api": "Int8Linear.forward + autograd backward, pinned host X and dY copied in every step"}
+        del xh, dyh, lin
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        ref = CpuReference(M, K, N, min(M, 512))
+        t_tok = statistics.median([ref.tokens_step() for _ in range(3)])
+        cpu_baseline = {"value": ref.tokens_per_s(t_tok), "unit": "tokens/s", "cores": ref.cores, "kind": "port",
+                        "sample": ref.describe(3), "t_weight_s": ref.t_weight, "t_tokens_s": t_tok}
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": "linear_fwd_bwd_tokens_per_s", "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": desc, "M": M, "K": K, "N": N, "N_per_gpu": Nl, "parallelism": f"tp{world}-column",
+                       "l2": "inputs (X 0.5 GB + dY >= 0.2 GB per step) exceed the 126 MB L2; no explicit flush"},
+            "tops_per_gpu": tops, "gemm_ms": {"fwd": t_fwd, "dx": t_dx, "dw": t_dw},
+            "roofline": roofline, "quantizers": quant, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "gpu_launches": 8 * args.steps, "clocks": clk.summary(),
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
