@@ -9,7 +9,7 @@ import ctypes
 import os
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG_DIR, "libi8linear.so")
+LIB_PATH = os.environ.get("I8L_LIBRARY_PATH") or os.path.join(_PKG_DIR, "libi8linear.so")
 
 OK = 0
 ERR_NAMES = {-1: "SHAPE", -2: "ALIGN", -3: "ARCH", -4: "CUDA", -5: "TIMEOUT", -6: "ARG"}

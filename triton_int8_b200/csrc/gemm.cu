@@ -1,12 +1,14 @@
 // INT8 GEMMs on the 5th-generation tensor cores: tcgen05.mma kind::i8 with int32 accumulators in
 // tensor memory, operands staged by TMA into a 128B-swizzled shared-memory ring.
 //
-// One persistent CTA per SM, 384 threads:
+// One persistent CTA per SM, 640 threads:
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      tensor-memory allocator + MMA issuer (one elected lane)
 //   warps 2-3   idle (they complete the first warpgroup so register budgets can be rebalanced)
-//   warps 4-11  epilogue: warp%4 selects the 32 accumulator lanes (rows) a warp may read, the
-//               warpgroup (4-7 / 8-11) selects columns 0-127 / 128-255 of the 128x256 tile.
+//   warps 4-19  epilogue: warp%4 selects the 32 accumulator lanes (rows) a warp may read, the
+//               group of four warps selects 64 of the 256 columns of the 128x256 tile.  Sixteen
+//               warps (four per scheduler) because the per-K-block drain is bound by instruction
+//               latency, not by a pipe: more resident warps hide it.
 // Tensor memory holds two 128x256 int32 accumulators (all 512 columns).  In block-scaled mode the
 // MMA warp alternates between them every 128-wide K block while the epilogue drains the other one
 // into fp32 registers (acc += float(P) * scale); in row x column mode a buffer holds a whole tile
@@ -17,15 +19,23 @@
 // and frees its tensor memory.
 #include <cuda.h>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 
 namespace i8l {
 
 constexpr int BM = 128, BN = 256, BK = 128;
-constexpr int STAGES = 4;
+#ifndef I8L_STAGES
+#define I8L_STAGES 4
+#endif
+constexpr int STAGES = I8L_STAGES;
 constexpr int A_STAGE = BM * BK;  // bytes
 constexpr int B_STAGE = BN * BK;
-constexpr int THREADS = 384;
+constexpr int EPI_WARPS = 16;                 // four groups of four warps, 64 accumulator columns per group
+constexpr int EPI_COLS = BN / (EPI_WARPS / 4);
+constexpr int THREADS = 128 + 32 * EPI_WARPS;
 constexpr int TMEM_COLS = 512;
 constexpr uint32_t STAGE_TX = A_STAGE + B_STAGE;
 constexpr int SMEM_DYN = STAGES * (A_STAGE + B_STAGE) + 1024;
@@ -75,16 +85,18 @@ __device__ __forceinline__ unsigned long long globaltimer() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait.  Returns false when the abort flag is (or becomes) set.
+// Bounded wait.  Returns false when the abort flag is (or becomes) set.  The wall-clock timer is
+// slow to read, so it stays off the fast path: it is first consulted after 4096 failed polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           unsigned long long limit_ns = WAIT_LIMIT_NS) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer();
-  for (uint32_t spin = 0;; ++spin) {
+  unsigned long long t0 = 0;
+  for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 63u) == 63u) {
+    if ((spin & 4095u) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer() - t0 > limit_ns) {
+      const unsigned long long now = globaltimer();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         return false;
       }
@@ -120,6 +132,15 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
         "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }
@@ -160,15 +181,63 @@ struct __align__(8) SharedCtl {
   uint64_t full[STAGES], empty[STAGES], tfull[2], tempty[2], done;
   uint32_t tmem_base;
   int abort_flag;
-  float bscale[2][128];     // per-tile column scales of each epilogue warpgroup (CHANNEL)
-  float bstep[2][2][128];   // per-K-block column scales (GROUP), double buffered
+  float bscale[EPI_WARPS / 4][EPI_COLS];     // per-tile column scales of each epilogue group (CHANNEL)
+  float bstep[EPI_WARPS / 4][2][EPI_COLS];   // per-K-block column scales (GROUP), double buffered
 };
 
-// BLOCK: drain the accumulator every 128-wide K block (block-scaled); otherwise once per tile.
-template <bool BLOCK>
+// Epilogue kinds.  Everything but K_ROWCOL drains the accumulator every 128-wide K block.
+constexpr int K_ROWCOL = 0;      // one drain per tile, (float(acc)*a_s[m])*b_s[n]
+constexpr int K_BLOCK_GEN = 1;   // block-scaled, any scale layout, reference operation order, dumps
+constexpr int K_BLOCK_FAST = 2;  // block-scaled, one scalar factor per (tile, K block) and 64-column group
+
+// Bit pattern of 1.5*2^23.  For |P| < 2^22, (P & 0x7FFFFF) ^ 0x4B400000 is the fp32 number
+// 12582912 + P exactly: one logic instruction instead of an int->float conversion (the conversion
+// unit is the slowest pipe of the SM).  A block partial satisfies |P| <= 128*128*128 = 2^21.
+constexpr uint32_t MAGIC_BITS = 0x4B400000u;
+constexpr float MAGIC_F = 12582912.0f;
+
+// (a & mask) ^ magic as one three-input logic instruction (truth table 0x6A for a=0xF0, b=0xCC, c=0xAA).
+__device__ __forceinline__ uint32_t magic1(uint32_t a, uint32_t mask, uint32_t magic) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(d) : "r"(a), "r"(mask), "r"(magic));
+  return d;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Final rescale, bias, cast and store of one thread's EPI_COLS consecutive columns.
+__device__ __forceinline__ void store_cols(const GemmParams& p, const float* acc, const float* bscale_or_null,
+                                           int64_t row, int col0) {
+#pragma unroll
+  for (int j0 = 0; j0 < EPI_COLS; j0 += 8) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      v[j] = acc[j0 + j];
+      if (bscale_or_null) v[j] *= bscale_or_null[j0 + j];
+      if (p.post_scale != 1.f) v[j] = __fmul_rn(v[j], p.post_scale);
+      if (p.bias) v[j] = __fadd_rn(v[j], __bfloat162float(p.bias[col0 + j0 + j]));
+    }
+    if (p.out_f32) {
+      float* o = static_cast<float*>(p.c) + row * p.N + col0 + j0;
+      *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+      __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.c) + row * p.N + col0 + j0;
+      *reinterpret_cast<uint4*>(o) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                                                pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+    }
+  }
+}
+
+template <int KIND>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const GemmParams p) {
+  constexpr bool BLOCK = KIND != K_ROWCOL;
   extern __shared__ uint8_t smem_raw[];
   __shared__ SharedCtl ctl;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -183,7 +252,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctl.tfull[b]), 1);
-      mbar_init(smem_u32(&ctl.tempty[b]), 8);  // one arrival per epilogue warp
+      mbar_init(smem_u32(&ctl.tempty[b]), EPI_WARPS);  // one arrival per epilogue warp
     }
     mbar_init(smem_u32(&ctl.done), 1);
     ctl.abort_flag = 0;
@@ -204,7 +273,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int KB = p.KB;
 
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0) {
       // ------------------------------------------------------------------ TMA producer
       int s = 0;
@@ -273,93 +342,140 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       mbar_wait(smem_u32(&ctl.done), 0, &dummy);
     }
   } else {
-    // -------------------------------------------------------------------- epilogue
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
-    const int q = warp & 3, wg = (warp - 4) >> 2;
-    const int tix = q * 32 + lane;  // row within the tile == thread index within the warpgroup
+    // -------------------------------------------------------------------- epilogue (16 warps)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+    const int q = warp & 3, wg = (warp - 4) >> 2;  // lane quarter, 64-column group
+    const int tix = q * 32 + lane;                 // row within the tile == thread index within the group
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     int ab = 0;
     uint32_t aph = 0;
     bool ok = true;
-    const bool fast_scalar = BLOCK && !p.exact && !p.divide && p.b_kind != I8L_BSCALE_GROUP && !p.dump;
+    auto release_accumulator = [&]() {  // all of this warp's tensor-memory loads of the buffer have completed
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctl.tempty[ab]));
+    };
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const TileCoord tc = tile_coord(t, p);
       const int batch = tc.m_blk / p.mpb;
       const int64_t row = (int64_t)tc.m_blk * BM + tix;  // row in the folded [batch*M] space
-      const int col0 = tc.n_tile * BN + wg * 128;
+      const int col0 = tc.n_tile * BN + wg * EPI_COLS;
       const bool active = col0 < p.N;
       const int64_t bcol0 = (int64_t)(p.b_batched ? batch : 0) * p.N + col0;  // first b_scale column index
-      if (BLOCK ? (p.b_kind == I8L_BSCALE_CHANNEL && !p.dump) : !p.dump) {
+      const bool chan = p.b_kind == I8L_BSCALE_CHANNEL && !p.dump;
+      if (chan) {  // K-invariant column scales of this group -> shared memory
         named_sync(1 + wg, 128);
-        ctl.bscale[wg][tix] = active ? __ldg(p.b_scale + bcol0 + tix) : 0.f;
+        if (tix < EPI_COLS) ctl.bscale[wg][tix] = active ? __ldg(p.b_scale + bcol0 + tix) : 0.f;
         named_sync(1 + wg, 128);
       }
-      float acc[BLOCK ? 128 : 1];
-      if (BLOCK) {
+
+      if constexpr (KIND == K_BLOCK_FAST) {
+        const float* as_ptr = p.a_scale + (p.a_kind == I8L_ASCALE_TILE ? (int64_t)tc.m_blk : row) * KB;
+        const float* bs_ptr = p.b_scale + (bcol0 >> 7) * KB;
+        float2 acc[EPI_COLS / 2];
 #pragma unroll
-        for (int j = 0; j < 128; ++j) acc[j] = 0.f;
-      }
-      const int ndrain = BLOCK ? KB : 1;
-      for (int d = 0; d < ndrain; ++d) {
-        float sa = 1.f, sb = 1.f;
-        if (BLOCK && !p.dump) {
-          sa = p.a_kind == I8L_ASCALE_TILE ? __ldg(p.a_scale + (int64_t)tc.m_blk * KB + d)
-                                           : __ldg(p.a_scale + row * KB + d);
-          if (p.b_kind == I8L_BSCALE_TILE && active) sb = __ldg(p.b_scale + (bcol0 >> 7) * KB + d);
-          if (p.b_kind == I8L_BSCALE_GROUP) {
-            ctl.bstep[wg][d & 1][tix] = active ? __ldg(p.b_scale + (bcol0 + tix) * KB + d) : 0.f;
-            named_sync(1 + wg, 128);
-          }
-        }
-        if (!(ok = mbar_wait(smem_u32(&ctl.tfull[ab]), aph, abort_flag))) break;
-        tc_fence_after();
-        const uint32_t taddr = tmem_base + lane_addr + ab * BN + wg * 128;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
+        for (int j = 0; j < EPI_COLS / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+        uint32_t mask_r = 0x7FFFFFu, magic_r = MAGIC_BITS;
+        asm volatile("" : "+r"(mask_r), "+r"(magic_r));  // keep both constants in registers
+        const float2 one2 = make_float2(1.f, 1.f), nmag2 = make_float2(-MAGIC_F, -MAGIC_F);
+        float f_next = __ldg(as_ptr) * ((!chan && active) ? __ldg(bs_ptr) : 1.f);
+        for (int d = 0; d < KB; ++d) {
+          const float f = f_next;
+          if (d + 1 < KB) f_next = __ldg(as_ptr + d + 1) * ((!chan && active) ? __ldg(bs_ptr + d + 1) : 1.f);
+          if (!(ok = mbar_wait(smem_u32(&ctl.tfull[ab]), aph, abort_flag))) break;
+          tc_fence_after();
           if (active) {
-            tc_ld32(taddr + c * 32, r);
-            tc_ld_wait();
-          }
-          if (c == 3) {  // accumulator fully read: hand the buffer back to the MMA warp
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctl.tempty[ab]));
-          }
-          if (!active) continue;
-          if (BLOCK) {
-            if (p.dump) {
-              int32_t* o = static_cast<int32_t*>(p.c) +
-                           (((int64_t)batch * KB + d) * p.M + (row - (int64_t)batch * p.M)) * p.N + col0 + c * 32;
+            const uint32_t taddr = tmem_base + lane_addr + ab * BN + wg * EPI_COLS;
+            const float2 f2 = make_float2(f, f);
 #pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-            } else if (fast_scalar) {
-              const float f = sa * sb;
+            for (int c = 0; c < EPI_COLS / 16; ++c) {
+              uint32_t r[16];
+              tc_ld16(taddr + c * 16, r);
+              tc_ld_wait();
+              if (c == EPI_COLS / 16 - 1) release_accumulator();
+              // three passes of independent instructions, in place: logic op, offset removal, accumulate
 #pragma unroll
-              for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(__int2float_rn((int)r[j]), f, acc[c * 32 + j]);
-            } else {
-              const float* sbv = p.b_kind == I8L_BSCALE_CHANNEL ? ctl.bscale[wg]
-                                 : p.b_kind == I8L_BSCALE_GROUP ? ctl.bstep[wg][d & 1]
-                                                                : nullptr;
+              for (int j = 0; j < 16; ++j) r[j] = magic1(r[j], mask_r, magic_r);
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const float pf = __int2float_rn((int)r[j]);
-                const float sbj = sbv ? sbv[c * 32 + j] : sb;
-                float term;
-                if (p.divide) term = __fdiv_rn(pf, __fmul_rn(sa, sbj));
-                else term = __fmul_rn(__fmul_rn(pf, sa), sbj);
-                acc[c * 32 + j] = __fadd_rn(acc[c * 32 + j], term);
+              for (int j = 0; j < 8; ++j) {
+                const float2 v = __ffma2_rn(make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), one2, nmag2);
+                acc[c * 8 + j] = __ffma2_rn(v, f2, acc[c * 8 + j]);
               }
             }
           } else {
-            // row x column epilogue straight from the accumulator chunk
-            if (p.dump) {
+            release_accumulator();
+          }
+          ab ^= 1;
+          if (ab == 0) aph ^= 1u;
+        }
+        if (ok && active) {
+          float out[EPI_COLS];
+#pragma unroll
+          for (int j = 0; j < EPI_COLS / 2; ++j) {
+            out[2 * j] = acc[j].x;
+            out[2 * j + 1] = acc[j].y;
+          }
+          store_cols(p, out, chan ? ctl.bscale[wg] : nullptr, row, col0);
+        }
+      } else {
+        // ---- generic paths: reference operation order, per-column / per-step scales, dumps, row x column
+        float acc[BLOCK ? EPI_COLS : 1];
+        if (BLOCK) {
+#pragma unroll
+          for (int j = 0; j < EPI_COLS; ++j) acc[j] = 0.f;
+        }
+        const int ndrain = BLOCK ? KB : 1;
+        for (int d = 0; d < ndrain; ++d) {
+          float sa = 1.f, sb = 1.f;
+          if (BLOCK && !p.dump) {
+            sa = p.a_kind == I8L_ASCALE_TILE ? __ldg(p.a_scale + (int64_t)tc.m_blk * KB + d)
+                                             : __ldg(p.a_scale + row * KB + d);
+            if (p.b_kind == I8L_BSCALE_TILE && active) sb = __ldg(p.b_scale + (bcol0 >> 7) * KB + d);
+            if (p.b_kind == I8L_BSCALE_GROUP) {
+              if (tix < EPI_COLS) ctl.bstep[wg][d & 1][tix] = active ? __ldg(p.b_scale + (bcol0 + tix) * KB + d) : 0.f;
+              named_sync(1 + wg, 128);
+            }
+          }
+          if (!(ok = mbar_wait(smem_u32(&ctl.tfull[ab]), aph, abort_flag))) break;
+          tc_fence_after();
+          const uint32_t taddr = tmem_base + lane_addr + ab * BN + wg * EPI_COLS;
+#pragma unroll
+          for (int c = 0; c < EPI_COLS / 32; ++c) {
+            uint32_t r[32];
+            if (active) {
+              tc_ld32(taddr + c * 32, r);
+              tc_ld_wait();
+            }
+            if (c == EPI_COLS / 32 - 1) release_accumulator();
+            if (!active) continue;
+            if (BLOCK) {
+              if (p.dump) {
+                int32_t* o = static_cast<int32_t*>(p.c) +
+                             (((int64_t)batch * KB + d) * p.M + (row - (int64_t)batch * p.M)) * p.N + col0 + c * 32;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                  *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+              } else {
+                const float* sbv = p.b_kind == I8L_BSCALE_CHANNEL ? ctl.bscale[wg]
+                                   : p.b_kind == I8L_BSCALE_GROUP ? ctl.bstep[wg][d & 1]
+                                                                  : nullptr;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  const float pf = __int2float_rn((int)r[j]);
+                  const float sbj = sbv ? sbv[c * 32 + j] : sb;
+                  float term;
+                  if (p.divide) term = __fdiv_rn(pf, __fmul_rn(sa, sbj));
+                  else term = __fmul_rn(__fmul_rn(pf, sa), sbj);
+                  acc[c * 32 + j] = __fadd_rn(acc[c * 32 + j], term);
+                }
+              }
+            } else if (p.dump) {
               int32_t* o = static_cast<int32_t*>(p.c) + row * p.N + col0 + c * 32;
 #pragma unroll
               for (int j = 0; j < 32; j += 4)
                 *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
             } else {
+              // row x column epilogue straight from the accumulator chunk
               const float sar = __ldg(p.a_scale + row);
               float v[32];
 #pragma unroll
@@ -379,46 +495,17 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               } else {
                 __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.c) + row * p.N + col0 + c * 32;
 #pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                  __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                  __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                  uint4 u;
-                  u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
-                  u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
-                  *reinterpret_cast<uint4*>(o + j) = u;
-                }
+                for (int j = 0; j < 32; j += 8)
+                  *reinterpret_cast<uint4*>(o + j) = make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
+                                                                pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
               }
             }
           }
+          ab ^= 1;
+          if (ab == 0) aph ^= 1u;
         }
-        ab ^= 1;
-        if (ab == 0) aph ^= 1u;
-      }
-      if (BLOCK && ok && active && !p.dump) {
-        const bool b_at_end = fast_scalar && p.b_kind == I8L_BSCALE_CHANNEL;
-#pragma unroll
-        for (int j0 = 0; j0 < 128; j0 += 8) {
-          float v[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            v[j] = acc[j0 + j];
-            if (b_at_end) v[j] *= ctl.bscale[wg][j0 + j];
-            if (p.post_scale != 1.f) v[j] = __fmul_rn(v[j], p.post_scale);
-            if (p.bias) v[j] = __fadd_rn(v[j], __bfloat162float(p.bias[col0 + j0 + j]));
-          }
-          if (p.out_f32) {
-            float* o = static_cast<float*>(p.c) + row * p.N + col0 + j0;
-            *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
-            *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
-          } else {
-            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.c) + row * p.N + col0 + j0;
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]), h3 = __floats2bfloat162_rn(v[6], v[7]);
-            uint4 u;
-            u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
-            u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
-            *reinterpret_cast<uint4*>(o) = u;
-          }
+        if constexpr (BLOCK) {
+          if (ok && active && !p.dump) store_cols(p, acc, nullptr, row, col0);
         }
       }
     }
@@ -474,6 +561,20 @@ static int sm_count() {
   return cached[dev];
 }
 
+template <int KIND>
+static int launch_kind(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int grid, cudaStream_t st) {
+  static bool attr_set[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    I8L_CUDA_OK(cudaFuncSetAttribute(gemm_i8_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
+    if (dev >= 0 && dev < 64) attr_set[dev] = true;
+  }
+  gemm_i8_kernel<KIND><<<grid, THREADS, SMEM_DYN, st>>>(ma, mb, p);
+  I8L_CUDA_OK(cudaGetLastError());
+  return I8L_OK;
+}
+
 static int launch_gemm(bool block, const int8_t* a_q, const int8_t* b_q, GemmParams p, int64_t batch, int64_t M,
                        int64_t N, int64_t K, cudaStream_t st) {
   if (batch <= 0 || M <= 0 || N <= 0 || K <= 0 || M % 128 || N % 128 || K % 128)
@@ -497,15 +598,10 @@ static int launch_gemm(bool block, const int8_t* a_q, const int8_t* b_q, GemmPar
   p.raster = 16;
   const int64_t tiles = (int64_t)p.m_blocks * p.n_tiles;
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  if (block) {
-    I8L_CUDA_OK(cudaFuncSetAttribute(gemm_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
-    gemm_i8_kernel<true><<<grid, THREADS, SMEM_DYN, st>>>(ma, mb, p);
-  } else {
-    I8L_CUDA_OK(cudaFuncSetAttribute(gemm_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
-    gemm_i8_kernel<false><<<grid, THREADS, SMEM_DYN, st>>>(ma, mb, p);
-  }
-  I8L_CUDA_OK(cudaGetLastError());
-  return I8L_OK;
+  if (!block) return launch_kind<K_ROWCOL>(ma, mb, p, grid, st);
+  const bool scalar_factor = !p.exact && !p.divide && !p.dump && p.b_kind != I8L_BSCALE_GROUP;
+  if (scalar_factor) return launch_kind<K_BLOCK_FAST>(ma, mb, p, grid, st);
+  return launch_kind<K_BLOCK_GEN>(ma, mb, p, grid, st);
 }
 
 }  // namespace i8l
