@@ -69,14 +69,16 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One poll.  The hint lets the hardware keep the thread suspended (off the issue slots) for up to
+// ~1 ms while the phase is incomplete; it resumes as soon as the phase completes.
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(1000000u)
       : "memory");
   return ok;
 }
@@ -86,13 +88,13 @@ __device__ __forceinline__ unsigned long long globaltimer() {
   return t;
 }
 // Bounded wait.  Returns false when the abort flag is (or becomes) set.  The wall-clock timer is
-// slow to read, so it stays off the fast path: it is first consulted after 4096 failed polls.
+// slow to read, so it stays off the fast path: it is first consulted after 256 failed polls (each poll may sleep).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           unsigned long long limit_ns = WAIT_LIMIT_NS) {
   unsigned long long t0 = 0;
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 4095u) == 0) {
+    if ((spin & 255u) == 0) {
       if (*abort_flag) return false;
       const unsigned long long now = globaltimer();
       if (t0 == 0) t0 = now;
@@ -190,18 +192,11 @@ constexpr int K_ROWCOL = 0;      // one drain per tile, (float(acc)*a_s[m])*b_s[
 constexpr int K_BLOCK_GEN = 1;   // block-scaled, any scale layout, reference operation order, dumps
 constexpr int K_BLOCK_FAST = 2;  // block-scaled, one scalar factor per (tile, K block) and 64-column group
 
-// Bit pattern of 1.5*2^23.  For |P| < 2^22, (P & 0x7FFFFF) ^ 0x4B400000 is the fp32 number
-// 12582912 + P exactly: one logic instruction instead of an int->float conversion (the conversion
-// unit is the slowest pipe of the SM).  A block partial satisfies |P| <= 128*128*128 = 2^21.
+// Bit pattern of 1.5*2^23.  For |P| < 2^22 the integer sum 0x4B400000 + P is the bit pattern of the
+// fp32 number 12582912 + P exactly: one integer add instead of an int->float conversion (the
+// conversion unit is the slowest pipe of the SM).  A block partial satisfies |P| <= 128*128*128 = 2^21.
 constexpr uint32_t MAGIC_BITS = 0x4B400000u;
 constexpr float MAGIC_F = 12582912.0f;
-
-// (a & mask) ^ magic as one three-input logic instruction (truth table 0x6A for a=0xF0, b=0xCC, c=0xAA).
-__device__ __forceinline__ uint32_t magic1(uint32_t a, uint32_t mask, uint32_t magic) {
-  uint32_t d;
-  asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(d) : "r"(a), "r"(mask), "r"(magic));
-  return d;
-}
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
@@ -375,9 +370,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         float2 acc[EPI_COLS / 2];
 #pragma unroll
         for (int j = 0; j < EPI_COLS / 2; ++j) acc[j] = make_float2(0.f, 0.f);
-        uint32_t mask_r = 0x7FFFFFu, magic_r = MAGIC_BITS;
-        asm volatile("" : "+r"(mask_r), "+r"(magic_r));  // keep both constants in registers
-        const float2 one2 = make_float2(1.f, 1.f), nmag2 = make_float2(-MAGIC_F, -MAGIC_F);
+        const uint32_t magic_r = MAGIC_BITS;
+        const float2 nmag2 = make_float2(-MAGIC_F, -MAGIC_F);
         float f_next = __ldg(as_ptr) * ((!chan && active) ? __ldg(bs_ptr) : 1.f);
         for (int d = 0; d < KB; ++d) {
           const float f = f_next;
@@ -393,12 +387,13 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               tc_ld16(taddr + c * 16, r);
               tc_ld_wait();
               if (c == EPI_COLS / 16 - 1) release_accumulator();
-              // three passes of independent instructions, in place: logic op, offset removal, accumulate
+              // integer add of the magic bits, packed subtract of the offset, packed multiply-accumulate:
+              // 2 instructions per accumulator element, each pass a run of independent instructions
 #pragma unroll
-              for (int j = 0; j < 16; ++j) r[j] = magic1(r[j], mask_r, magic_r);
+              for (int j = 0; j < 16; ++j) r[j] += magic_r;  // bits of 12582912 + P (exact for |P| < 2^22)
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
-                const float2 v = __ffma2_rn(make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), one2, nmag2);
+                const float2 v = __fadd2_rn(make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), nmag2);
                 acc[c * 8 + j] = __ffma2_rn(v, f2, acc[c * 8 + j]);
               }
             }
