@@ -90,6 +90,25 @@ I8L_API int i8l_quant_row(const void* x, int64_t rows, int64_t cols, int qmode, 
 I8L_API int i8l_quant_col_t(const void* x, int64_t rows, int64_t cols, int qmode, int8_t* qt, float* scale_t,
                     float* colmax_scratch, void* stream);
 
+/*
+ * Same result as i8l_quant_col_t, for callers that cannot hand over scratch memory: code running
+ * where device allocation is off limits (inside a framework's memory-pool callback or a stream
+ * capture section, in a plugin sandbox that forbids cudaMalloc, or late in a job when the pool is
+ * exhausted) still has to quantise W^T for the dX GEMM.  The column-absmax scratch is a fixed
+ * array of I8L_STATIC_SCRATCH_MAX_COLS floats (256 KiB) built into the library image; every GPU
+ * that loads the library holds it until the process exits.  No counterpart in the reference.
+ *   - cols > I8L_STATIC_SCRATCH_MAX_COLS is rejected with I8L_ERR_SHAPE.
+ *   - The first call on each device resolves the array's device address (a synchronous runtime
+ *     query made with that device current); make that first call before any stream capture.
+ *   - Nothing is allocated or freed, by this function or by anything it calls.
+ *   - All calls on a device share the one array; it is re-zeroed on the given stream at the start
+ *     of every call, so back-to-back calls on one stream are safe, but two calls whose kernels
+ *     may overlap on the GPU (different streams) race on it and give wrong scales.
+ */
+#define I8L_STATIC_SCRATCH_MAX_COLS 65536
+I8L_API int i8l_quant_col_t_static(const void* x, int64_t rows, int64_t cols, int qmode, int8_t* qt,
+                                   float* scale_t, void* stream);
+
 /* Scale layouts understood by the GEMM. */
 #define I8L_ASCALE_TILE 0  /* a_scale fp32 [batch, M/128, K/128] */
 #define I8L_ASCALE_GROUP 1 /* a_scale fp32 [batch, M, K/128]     */

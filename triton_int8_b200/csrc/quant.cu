@@ -494,3 +494,28 @@ extern "C" int i8l_quant_col_t(const void* x, int64_t rows, int64_t cols, int qm
 #undef I8L_COL_CASE
   return fail(I8L_ERR_ARG, "i8l_quant_col_t: unsupported qmode=%d", qmode);
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant of i8l_quant_col_t: the column-absmax scratch lives in a file-scope device
+// array instead of caller memory.  In host code `g_colmax_static` is only a stand-in symbol, not a
+// device address; the real address is looked up once per device with cudaGetSymbolAddress (with
+// that device current) and cached.
+// ------------------------------------------------------------------------------------------------
+static __device__ __align__(256) float g_colmax_static[I8L_STATIC_SCRATCH_MAX_COLS];
+static float* g_colmax_static_addr[64];  // per device ordinal, nullptr = not looked up yet
+
+extern "C" int i8l_quant_col_t_static(const void* x, int64_t rows, int64_t cols, int qmode, int8_t* qt,
+                                      float* scale_t, void* stream) {
+  if (cols > I8L_STATIC_SCRATCH_MAX_COLS)
+    return fail(I8L_ERR_SHAPE, "i8l_quant_col_t_static: cols=%lld exceeds the built-in scratch of %d columns; "
+                "use i8l_quant_col_t with caller-provided scratch", (long long)cols, I8L_STATIC_SCRATCH_MAX_COLS);
+  int dev = 0;
+  I8L_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(I8L_ERR_ARG, "device ordinal %d out of range", dev);
+  if (!g_colmax_static_addr[dev]) {
+    float* ptr = nullptr;
+    I8L_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_colmax_static));
+    g_colmax_static_addr[dev] = ptr;
+  }
+  return i8l_quant_col_t(x, rows, cols, qmode, qt, scale_t, g_colmax_static_addr[dev], stream);
+}
