@@ -76,7 +76,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+                                          "-i", str(self.index), "-lms", "50"], stdout=subprocess.PIPE, text=True)
             self.t = threading.Thread(target=lambda: [self.lines.append(l) for l in self.proc.stdout], daemon=True)
             self.t.start()
         except Exception:
@@ -92,13 +92,13 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         for l in self.lines:
             f = [t.strip() for t in l.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
+                sm.append(float(f[1])); mx.append(float(f[2])); pw.append(float(f[3]))
             except ValueError:
                 continue
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
@@ -106,8 +106,9 @@ class ClockSampler:
                     reasons.add(name)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
-        busy = sorted(sm)[len(sm) // 2:]  # upper half = samples under load
-        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        load = [c for c, w in zip(sm, pw) if w >= 0.6 * max(pw)] or sm   # samples taken under load (by power draw)
+        return {"sm_mhz": statistics.median(load), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm), "samples_under_load": len(load), "power_w_max": max(pw)}
 
 
 class CpuReference:
@@ -255,18 +256,16 @@ def main():
             gemm_events.append(e)
         return y, dx, dw
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    sync_all()
     t0, t1 = ev(), ev()
     with ClockSampler(local_rank) as clk:
-        time.sleep(0.25)
+        for _ in range(max(args.warmup, 3)):
+            step()
+        sync_all()
         t0.record()
         for _ in range(args.steps):
             out = step(record=True)
         t1.record()
         sync_all()
-        time.sleep(0.15)
     ms = t0.elapsed_time(t1)
     if world > 1:
         tms = torch.tensor([ms], device=dev)
@@ -331,9 +330,12 @@ def main():
             lin.weight.copy_(w)
         res_h = torch.empty(3, dtype=torch.float32).pin_memory()
 
+        from triton_int8_b200.hostio import HostPrefetcher
+        feed = HostPrefetcher(lambda: (xh, dyh), dev)   # every step copies X and dY from pinned host memory
+
         def e2e_step():
-            xd = xh.to(dev, non_blocking=True).requires_grad_(True)
-            dyd = dyh.to(dev, non_blocking=True)
+            xd, dyd = feed.get()                         # copy of the next step overlaps this step's compute
+            xd = xd.detach().requires_grad_(True)
             yy = lin(xd)
             yy.backward(dyd)
             dxp = xd.grad
@@ -341,6 +343,7 @@ def main():
                 dxp = tp.reduce_scatter_rows(dxp)
             r = torch.stack([yy[0, :128].float().sum(), dxp[0, :128].float().sum(), lin.weight.grad[0, :128].float().sum()])
             res_h.copy_(r, non_blocking=True)
+            feed.done()
             lin.weight.grad = None
         n_e2e = max(2, min(args.steps, 5))
         e2e_step(); sync_all()
@@ -356,7 +359,7 @@ def main():
             ems = tms.item()
         e2e = {"value": M / (ems / n_e2e * 1e-3), "unit": "tokens/s",
                "h2d_bytes_per_step": xh.numel() * 2 + dyh.numel() * 2, "d2h_bytes_per_step": 12,
-               "api": "Int8Linear.forward + autograd backward, pinned host X and dY copied in every step"}
+               "api": "Int8Linear.forward + autograd backward; X and dY copied from pinned host memory every step, copy of step i+1 overlapped with step i (HostPrefetcher)"}
         del xh, dyh, lin
 
     cpu_baseline = None

@@ -88,7 +88,7 @@ __device__ __forceinline__ unsigned long long globaltimer() {
   return t;
 }
 // Bounded wait.  Returns false when the abort flag is (or becomes) set.  The wall-clock timer is
-// slow to read, so it stays off the fast path: it is first consulted after 256 failed polls (each poll may sleep).
+// slow to read, so it stays off the fast path: it is first consulted after 256 failed polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           unsigned long long limit_ns = WAIT_LIMIT_NS) {
   unsigned long long t0 = 0;
@@ -191,12 +191,6 @@ struct __align__(8) SharedCtl {
 constexpr int K_ROWCOL = 0;      // one drain per tile, (float(acc)*a_s[m])*b_s[n]
 constexpr int K_BLOCK_GEN = 1;   // block-scaled, any scale layout, reference operation order, dumps
 constexpr int K_BLOCK_FAST = 2;  // block-scaled, one scalar factor per (tile, K block) and 64-column group
-
-// Bit pattern of 1.5*2^23.  For |P| < 2^22 the integer sum 0x4B400000 + P is the bit pattern of the
-// fp32 number 12582912 + P exactly: one integer add instead of an int->float conversion (the
-// conversion unit is the slowest pipe of the SM).  A block partial satisfies |P| <= 128*128*128 = 2^21.
-constexpr uint32_t MAGIC_BITS = 0x4B400000u;
-constexpr float MAGIC_F = 12582912.0f;
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
@@ -370,8 +364,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         float2 acc[EPI_COLS / 2];
 #pragma unroll
         for (int j = 0; j < EPI_COLS / 2; ++j) acc[j] = make_float2(0.f, 0.f);
-        const uint32_t magic_r = MAGIC_BITS;
-        const float2 nmag2 = make_float2(-MAGIC_F, -MAGIC_F);
         float f_next = __ldg(as_ptr) * ((!chan && active) ? __ldg(bs_ptr) : 1.f);
         for (int d = 0; d < KB; ++d) {
           const float f = f_next;
@@ -387,15 +379,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               tc_ld16(taddr + c * 16, r);
               tc_ld_wait();
               if (c == EPI_COLS / 16 - 1) release_accumulator();
-              // integer add of the magic bits, packed subtract of the offset, packed multiply-accumulate:
-              // 2 instructions per accumulator element, each pass a run of independent instructions
+              // one conversion and half a packed FMA per accumulator element; each pass is a run of
+              // independent instructions
+              float v[16];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) r[j] += magic_r;  // bits of 12582912 + P (exact for |P| < 2^22)
+              for (int j = 0; j < 16; ++j) v[j] = __int2float_rn((int)r[j]);
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float2 v = __fadd2_rn(make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), nmag2);
-                acc[c * 8 + j] = __ffma2_rn(v, f2, acc[c * 8 + j]);
-              }
+              for (int j = 0; j < 8; ++j)
+                acc[c * 8 + j] = __ffma2_rn(make_float2(v[2 * j], v[2 * j + 1]), f2, acc[c * 8 + j]);
             }
           } else {
             release_accumulator();
@@ -435,62 +426,62 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tc_fence_after();
           const uint32_t taddr = tmem_base + lane_addr + ab * BN + wg * EPI_COLS;
 #pragma unroll
-          for (int c = 0; c < EPI_COLS / 32; ++c) {
-            uint32_t r[32];
+          for (int c = 0; c < EPI_COLS / 16; ++c) {
+            uint32_t r[16];
             if (active) {
-              tc_ld32(taddr + c * 32, r);
+              tc_ld16(taddr + c * 16, r);
               tc_ld_wait();
             }
-            if (c == EPI_COLS / 32 - 1) release_accumulator();
+            if (c == EPI_COLS / 16 - 1) release_accumulator();
             if (!active) continue;
             if (BLOCK) {
               if (p.dump) {
                 int32_t* o = static_cast<int32_t*>(p.c) +
-                             (((int64_t)batch * KB + d) * p.M + (row - (int64_t)batch * p.M)) * p.N + col0 + c * 32;
+                             (((int64_t)batch * KB + d) * p.M + (row - (int64_t)batch * p.M)) * p.N + col0 + c * 16;
 #pragma unroll
-                for (int j = 0; j < 32; j += 4)
+                for (int j = 0; j < 16; j += 4)
                   *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
               } else {
                 const float* sbv = p.b_kind == I8L_BSCALE_CHANNEL ? ctl.bscale[wg]
                                    : p.b_kind == I8L_BSCALE_GROUP ? ctl.bstep[wg][d & 1]
                                                                   : nullptr;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
+                for (int j = 0; j < 16; ++j) {
                   const float pf = __int2float_rn((int)r[j]);
-                  const float sbj = sbv ? sbv[c * 32 + j] : sb;
+                  const float sbj = sbv ? sbv[c * 16 + j] : sb;
                   float term;
                   if (p.divide) term = __fdiv_rn(pf, __fmul_rn(sa, sbj));
                   else term = __fmul_rn(__fmul_rn(pf, sa), sbj);
-                  acc[c * 32 + j] = __fadd_rn(acc[c * 32 + j], term);
+                  acc[c * 16 + j] = __fadd_rn(acc[c * 16 + j], term);
                 }
               }
             } else if (p.dump) {
-              int32_t* o = static_cast<int32_t*>(p.c) + row * p.N + col0 + c * 32;
+              int32_t* o = static_cast<int32_t*>(p.c) + row * p.N + col0 + c * 16;
 #pragma unroll
-              for (int j = 0; j < 32; j += 4)
+              for (int j = 0; j < 16; j += 4)
                 *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
             } else {
               // row x column epilogue straight from the accumulator chunk
               const float sar = __ldg(p.a_scale + row);
-              float v[32];
+              float v[16];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                v[j] = __fmul_rn(__fmul_rn(__int2float_rn((int)r[j]), sar), ctl.bscale[wg][c * 32 + j]);
+              for (int j = 0; j < 16; ++j) {
+                v[j] = __fmul_rn(__fmul_rn(__int2float_rn((int)r[j]), sar), ctl.bscale[wg][c * 16 + j]);
                 if (!p.out_f32 && (p.post_scale != 1.f || p.bias)) {
                   v[j] = round_to_bf16(v[j]);  // the reference rounds to bf16 before its 1/K pass
                   v[j] = __fmul_rn(v[j], p.post_scale);
-                  if (p.bias) v[j] = __fadd_rn(v[j], __bfloat162float(p.bias[col0 + c * 32 + j]));
+                  if (p.bias) v[j] = __fadd_rn(v[j], __bfloat162float(p.bias[col0 + c * 16 + j]));
                 }
               }
               if (p.out_f32) {
-                float* o = static_cast<float*>(p.c) + row * p.N + col0 + c * 32;
+                float* o = static_cast<float*>(p.c) + row * p.N + col0 + c * 16;
 #pragma unroll
-                for (int j = 0; j < 32; j += 4)
+                for (int j = 0; j < 16; j += 4)
                   *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
               } else {
-                __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.c) + row * p.N + col0 + c * 32;
+                __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.c) + row * p.N + col0 + c * 16;
 #pragma unroll
-                for (int j = 0; j < 32; j += 8)
+                for (int j = 0; j < 16; j += 8)
                   *reinterpret_cast<uint4*>(o + j) = make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
                                                                 pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
               }
