@@ -581,7 +581,12 @@ static int launch_gemm(bool block, const int8_t* a_q, const int8_t* b_q, GemmPar
   p.M = (int)M;
   p.N = (int)N;
   p.KB = (int)(K / 128);
-  p.raster = 16;
+  // M-blocks per raster group: the group's A panel (raster x 128 x K bytes) should stay L2-resident
+  // while the CTAs sweep the N tiles (measured best: 32 blocks at K = 8192, flat for deeper K).
+  {
+    const int64_t fit = (32ll << 20) / (128 * K);
+    p.raster = (int)(fit < 8 ? 8 : (fit > 32 ? 32 : fit));
+  }
   const int64_t tiles = (int64_t)p.m_blocks * p.n_tiles;
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
   if (!block) return launch_kind<K_ROWCOL>(ma, mb, p, grid, st);

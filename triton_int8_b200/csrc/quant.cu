@@ -45,8 +45,17 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
          ((uint32_t)(d & 0xff) << 24);
 }
 
+// |x| maximum of the 8 bf16 values of a 16-byte vector, as two packed maxima (exact: bf16 compare).
+__device__ __forceinline__ __nv_bfloat162 absmax8(const uint4& u, __nv_bfloat162 m) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) m = __hmax2(m, __habs2(h[k]));
+  return m;
+}
+__device__ __forceinline__ float hmax_of(__nv_bfloat162 m) { return fmaxf(__low2float(m), __high2float(m)); }
+
 template <int GRAN, int MODE, bool HAD, bool OUT_N, bool OUT_T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 quant_tile_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t cols,
                   int8_t* __restrict__ q, float* __restrict__ scale, int8_t* __restrict__ qt,
                   float* __restrict__ scale_t, const float* __restrict__ colmax) {
@@ -60,33 +69,37 @@ quant_tile_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t col
   const int64_t boff = (int64_t)blockIdx.z * rows * cols;
   const __nv_bfloat16* xb = x + boff;
 
-  float v[2][4][8];
+  // The tile stays in registers as packed bf16 (32 registers per thread, 4 CTAs per SM); with the
+  // Hadamard rotation the rotated values, already rounded to bf16, replace the raw ones.
+  uint4 raw[2][4];
 #pragma unroll
   for (int it = 0; it < 2; ++it)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int r = 16 * w + 8 * it + 4 * half + i;
-      const uint4 u = __ldg(reinterpret_cast<const uint4*>(xb + (r_base + r) * cols + c_base + 8 * cc));
-      unpack8(u, v[it][i]);
+      raw[it][i] = __ldg(reinterpret_cast<const uint4*>(xb + (r_base + r) * cols + c_base + 8 * cc));
       if (HAD) {
-        fwht128_lanes16(v[it][i], l);
+        float v[8];
+        unpack8(raw[it][i], v);
+        fwht128_lanes16(v, l);
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw[it][i]);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[it][i][j] = round_to_bf16(v[it][i][j]);
+        for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
       }
     }
 
   // ---- scales
+  const __nv_bfloat162 zero2 = __floats2bfloat162_rn(0.f, 0.f);
   float s_tile = 0.f;          // TILE128
   float s_row[2][4];           // GROUP128 natural
   float s_col[8];              // column scales (GROUP128 transposed / COLFULL)
   if (GRAN == I8L_GRAN_TILE128) {
-    float m = 0.f;
+    __nv_bfloat162 m2 = zero2;
 #pragma unroll
     for (int it = 0; it < 2; ++it)
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(v[it][i][j]));
+      for (int i = 0; i < 4; ++i) m2 = absmax8(raw[it][i], m2);
+    float m = hmax_of(m2);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     if (l == 0) s_red[w] = m;
@@ -106,9 +119,7 @@ quant_tile_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t col
     for (int it = 0; it < 2; ++it)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        float m = 0.f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(v[it][i][j]));
+        float m = hmax_of(absmax8(raw[it][i], zero2));
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
         float stored;
@@ -120,13 +131,18 @@ quant_tile_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t col
       }
   } else {  // column scales
     if (GRAN == I8L_GRAN_GROUP128) {
+      __nv_bfloat162 cm[4] = {zero2, zero2, zero2, zero2};   // per-column maxima of this thread's 8 rows
+#pragma unroll
+      for (int it = 0; it < 2; ++it)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[it][i]);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) cm[k] = __hmax2(cm[k], __habs2(h[k]));
+        }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        float m = 0.f;
-#pragma unroll
-        for (int it = 0; it < 2; ++it)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) m = fmaxf(m, fabsf(v[it][i][j]));
+        float m = (j & 1) ? __high2float(cm[j >> 1]) : __low2float(cm[j >> 1]);
         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
         if (half == 0) s_colred[w * 128 + 8 * cc + j] = m;
       }
@@ -159,15 +175,18 @@ quant_tile_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t col
   for (int it = 0; it < 2; ++it) {
     int b[4][8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 4; ++i) {
+      float v[8];
+      unpack8(raw[it][i], v);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         float s;
         if (GRAN == I8L_GRAN_TILE128) s = s_tile;
         else if (GRAN == I8L_GRAN_GROUP128 && OUT_N) s = s_row[it][i];
         else s = s_col[j];
-        b[i][j] = quant1<MODE>(v[it][i][j], s);
+        b[i][j] = quant1<MODE>(v[j], s);
       }
+    }
     if (OUT_N) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
