@@ -30,15 +30,21 @@ constexpr int BM = 128, BN = 256, BK = 128;
 #ifndef I8L_STAGES
 #define I8L_STAGES 4
 #endif
-constexpr int STAGES = I8L_STAGES;
 constexpr int A_STAGE = BM * BK;  // bytes
-constexpr int B_STAGE = BN * BK;
+// One CTA per tile: 128x256 tile, 4 stages of 16 KB (A) + 32 KB (B).
+// CTA pair per tile (cta_group::2): 256x256 tile, each CTA stages its own 128 rows of A and 128 of the
+// 256 rows of B (16 KB + 16 KB), 6 stages: half the B traffic through each SM's shared memory.
+template <bool TWO> struct Cfg {
+  static constexpr int STAGES = TWO ? 6 : I8L_STAGES;
+  static constexpr int B_STAGE = TWO ? BM * BK : BN * BK;
+  static constexpr uint32_t STAGE_TX = TWO ? 2u * (A_STAGE + BM * BK) : (uint32_t)(A_STAGE + BN * BK);
+};
+constexpr int MAX_STAGES = 6;
 constexpr int EPI_WARPS = 16;                 // four groups of four warps, 64 accumulator columns per group
 constexpr int EPI_COLS = BN / (EPI_WARPS / 4);
 constexpr int THREADS = 128 + 32 * EPI_WARPS;
 constexpr int TMEM_COLS = 512;
-constexpr uint32_t STAGE_TX = A_STAGE + B_STAGE;
-constexpr int SMEM_DYN = STAGES * (A_STAGE + B_STAGE) + 1024;
+constexpr int SMEM_DYN = 4 * (A_STAGE + BN * BK) + 1024;  // == 6 * (16 KB + 16 KB) + 1024
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
 struct GemmParams {
@@ -111,6 +117,48 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+// --- CTA-pair (cta_group::2) variants ---------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load whose completion is signalled on a barrier of either CTA of the pair (no multicast).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {  // arrives on `bar` in both CTAs of the pair
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((uint16_t)3)
+               : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair_local(uint32_t bar) {  // arrives on the executing CTA's barrier only
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -164,15 +212,18 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
 // Instruction descriptor: D=s32, A=B=s8, both K-major, M=128, N=256, dense, no saturation.
 constexpr uint32_t IDESC_I8 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
                               ((uint32_t)(BM >> 4) << 24);
+// Same with M=256 for the CTA-pair instruction (128 rows per CTA).
+constexpr uint32_t IDESC_I8_PAIR = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                   ((uint32_t)((2 * BM) >> 4) << 24);
 
 struct TileCoord {
   int m_blk, n_tile;
 };
-__device__ __forceinline__ TileCoord tile_coord(int t, const GemmParams& p) {
+__device__ __forceinline__ TileCoord tile_coord(int t, int m_units, const GemmParams& p) {
   const int per_group = p.raster * p.n_tiles;
   const int g = t / per_group, local = t - g * per_group;
   const int first = g * p.raster;
-  const int gsize = min(p.raster, p.m_blocks - first);
+  const int gsize = min(p.raster, m_units - first);
   TileCoord tc;
   tc.m_blk = first + local % gsize;
   tc.n_tile = local / gsize;
@@ -180,7 +231,7 @@ __device__ __forceinline__ TileCoord tile_coord(int t, const GemmParams& p) {
 }
 
 struct __align__(8) SharedCtl {
-  uint64_t full[STAGES], empty[STAGES], tfull[2], tempty[2], done;
+  uint64_t full[MAX_STAGES], empty[MAX_STAGES], tfull[2], tempty[2], done;
   uint32_t tmem_base;
   int abort_flag;
   float bscale[EPI_WARPS / 4][EPI_COLS];     // per-tile column scales of each epilogue group (CHANNEL)
@@ -222,17 +273,24 @@ __device__ __forceinline__ void store_cols(const GemmParams& p, const float* acc
   }
 }
 
-template <int KIND>
+template <int KIND, bool TWO>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const GemmParams p) {
   constexpr bool BLOCK = KIND != K_ROWCOL;
+  constexpr int STAGES = Cfg<TWO>::STAGES, B_STAGE = Cfg<TWO>::B_STAGE;
+  constexpr uint32_t STAGE_TX = Cfg<TWO>::STAGE_TX;
   extern __shared__ uint8_t smem_raw[];
   __shared__ SharedCtl ctl;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t smem_a = smem_base, smem_b = smem_base + STAGES * A_STAGE;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &ctl.abort_flag;
+  // CTA pair: rank 0 (the leader) owns the operand-ready and accumulator-free barriers and issues the MMAs
+  const uint32_t rank = TWO ? cluster_ctarank() : 0u;
+  const bool leader = rank == 0;
+  const int unit = TWO ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;      // tile-processing unit (CTA or pair)
+  const int n_units = TWO ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -241,7 +299,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctl.tfull[b]), 1);
-      mbar_init(smem_u32(&ctl.tempty[b]), EPI_WARPS);  // one arrival per epilogue warp
+      mbar_init(smem_u32(&ctl.tempty[b]), (TWO ? 2 : 1) * EPI_WARPS);  // one arrival per epilogue warp (of both CTAs)
     }
     mbar_init(smem_u32(&ctl.done), 1);
     ctl.abort_flag = 0;
@@ -249,16 +307,30 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl.tmem_base)),
-                 "r"(TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (TWO) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl.tmem_base)),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl.tmem_base)),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (TWO) cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = ctl.tmem_base;
-  const int total_tiles = p.m_blocks * p.n_tiles;
+  // tiles of this unit: m_blocks counts 128-row blocks; a pair takes two consecutive ones
+  const int total_tiles = (TWO ? p.m_blocks / 2 : p.m_blocks) * p.n_tiles;
+  auto unit_tile = [&](int t) {  // 128-row block of THIS CTA and 256-column tile
+    TileCoord tc = tile_coord(t, TWO ? p.m_blocks / 2 : p.m_blocks, p);
+    if (TWO) tc.m_blk = 2 * tc.m_blk + (int)rank;
+    return tc;
+  };
   const int KB = p.KB;
 
   if (warp < 4) {
@@ -269,24 +341,31 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       uint32_t ph = 0;
       uint32_t issued = 0, issued_ph = 0;  // bit s: a load into stage s is (or was) in flight, with parity
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const TileCoord tc = tile_coord(t, p);
+      for (int t = unit; t < total_tiles && ok; t += n_units) {
+        const TileCoord tc = unit_tile(t);
         const int a_row = tc.m_blk * BM;
-        const int b_row = (p.b_batched ? (tc.m_blk / p.mpb) * p.N : 0) + tc.n_tile * BN;
+        const int b_row = (p.b_batched ? (tc.m_blk / p.mpb) * p.N : 0) + tc.n_tile * BN + (TWO ? (int)rank * BM : 0);
         for (int kb = 0; kb < KB; ++kb) {
           if (!(ok = mbar_wait(smem_u32(&ctl.empty[s]), ph ^ 1u, abort_flag))) break;
           if (lane == 0) {
             const uint32_t bar = smem_u32(&ctl.full[s]);
-            mbar_expect_tx(bar, STAGE_TX);
-            tma_load_2d(smem_a + s * A_STAGE, &map_a, bar, kb * BK, a_row);
-            tma_load_2d(smem_b + s * B_STAGE, &map_b, bar, kb * BK, b_row);
+            if (TWO) {  // both CTAs' copies complete on the leader's barrier, which expects the bytes of both
+              if (leader) mbar_expect_tx(bar, STAGE_TX);
+              const uint32_t lbar = map_to_cta(bar, 0);
+              tma_load_2d_pair(smem_a + s * A_STAGE, &map_a, lbar, kb * BK, a_row);
+              tma_load_2d_pair(smem_b + s * B_STAGE, &map_b, lbar, kb * BK, b_row);
+            } else {
+              mbar_expect_tx(bar, STAGE_TX);
+              tma_load_2d(smem_a + s * A_STAGE, &map_a, bar, kb * BK, a_row);
+              tma_load_2d(smem_b + s * B_STAGE, &map_b, bar, kb * BK, b_row);
+            }
           }
           issued |= 1u << s;
           issued_ph = (issued_ph & ~(1u << s)) | (ph << s);
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
       }
-      if (!ok) {
+      if (!ok && leader) {
         // let copies already in flight land before the CTA's shared memory is released
         for (int k = 0; k < STAGES; ++k)
           if (issued & (1u << k)) {
@@ -294,12 +373,12 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_wait(smem_u32(&ctl.full[k]), (issued_ph >> k) & 1u, &dummy, 100000000ull);
           }
       }
-    } else if (warp == 1) {
+    } else if (warp == 1 && leader) {
       // ------------------------------------------------------------------ MMA issuer
       int s = 0, ab = 0;
       uint32_t ph = 0, aph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < total_tiles && ok; t += n_units) {
         for (int kb = 0; kb < KB; ++kb) {
           const bool drain_start = BLOCK || kb == 0, drain_end = BLOCK || kb == KB - 1;
           if (drain_start) {
@@ -311,10 +390,17 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint64_t da = smem_desc(smem_a + s * A_STAGE), db = smem_desc(smem_b + s * B_STAGE);
             const uint32_t d = tmem_base + ab * BN;
 #pragma unroll
-            for (int k4 = 0; k4 < BK / 32; ++k4)
-              tc_mma_i8(d, da + 2 * k4, db + 2 * k4, IDESC_I8, (k4 > 0 || !drain_start) ? 1u : 0u);
-            tc_commit(smem_u32(&ctl.empty[s]));
-            if (drain_end) tc_commit(smem_u32(&ctl.tfull[ab]));
+            for (int k4 = 0; k4 < BK / 32; ++k4) {
+              if (TWO) tc_mma_i8_pair(d, da + 2 * k4, db + 2 * k4, IDESC_I8_PAIR, (k4 > 0 || !drain_start) ? 1u : 0u);
+              else tc_mma_i8(d, da + 2 * k4, db + 2 * k4, IDESC_I8, (k4 > 0 || !drain_start) ? 1u : 0u);
+            }
+            if (TWO) {  // both CTAs' producers and epilogues wait on their own copies of these barriers
+              tc_commit_pair(smem_u32(&ctl.empty[s]));
+              if (drain_end) tc_commit_pair(smem_u32(&ctl.tfull[ab]));
+            } else {
+              tc_commit(smem_u32(&ctl.empty[s]));
+              if (drain_end) tc_commit(smem_u32(&ctl.tfull[ab]));
+            }
           }
           __syncwarp();
           if (drain_end) {
@@ -325,7 +411,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
       // all MMAs issued by this thread must have retired before tensor memory is freed
-      if (lane == 0) tc_commit(smem_u32(&ctl.done));
+      if (lane == 0) {
+        if (TWO) tc_commit_pair_local(smem_u32(&ctl.done));
+        else tc_commit(smem_u32(&ctl.done));
+      }
       __syncwarp();
       int dummy = 0;
       mbar_wait(smem_u32(&ctl.done), 0, &dummy);
@@ -342,10 +431,13 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     auto release_accumulator = [&]() {  // all of this warp's tensor-memory loads of the buffer have completed
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ctl.tempty[ab]));
+      if (lane == 0) {
+        if (TWO) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl.tempty[ab]), 0));  // the leader's barrier
+        else mbar_arrive(smem_u32(&ctl.tempty[ab]));
+      }
     };
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const TileCoord tc = tile_coord(t, p);
+    for (int t = unit; t < total_tiles && ok; t += n_units) {
+      const TileCoord tc = unit_tile(t);
       const int batch = tc.m_blk / p.mpb;
       const int64_t row = (int64_t)tc.m_blk * BM + tix;  // row in the folded [batch*M] space
       const int col0 = tc.n_tile * BN + wg * EPI_COLS;
@@ -499,10 +591,12 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   tc_fence_before();
   __syncthreads();
+  if (TWO) cluster_sync_all();  // no remote arrival or tensor-memory write of the pair is still pending
   if (threadIdx.x == 0 && ctl.abort_flag && p.status) atomicExch(p.status, I8L_ERR_TIMEOUT);
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if (TWO) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -547,18 +641,51 @@ static int sm_count() {
   return cached[dev];
 }
 
-template <int KIND>
-static int launch_kind(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int grid, cudaStream_t st) {
+template <int KIND, bool TWO>
+static int launch_kind(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int64_t tiles, cudaStream_t st) {
   static bool attr_set[64];
+  static int max_clusters[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-    I8L_CUDA_OK(cudaFuncSetAttribute(gemm_i8_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
-    if (dev >= 0 && dev < 64) attr_set[dev] = true;
+  if (dev < 0 || dev >= 64) dev = 0;
+  auto kernel = gemm_i8_kernel<KIND, TWO>;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  cfg.blockDim = dim3(THREADS, 1, 1);
+  cfg.dynamicSmemBytes = SMEM_DYN;
+  cfg.stream = st;
+  if (TWO) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
   }
-  gemm_i8_kernel<KIND><<<grid, THREADS, SMEM_DYN, st>>>(ma, mb, p);
-  I8L_CUDA_OK(cudaGetLastError());
+  if (!attr_set[dev]) {
+    I8L_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
+    if (TWO) {  // how many CTA pairs can be co-resident (GPCs with an odd SM count leave one SM unpaired)
+      cfg.gridDim = dim3(2 * sm_count(), 1, 1);
+      int n = 0;
+      I8L_CUDA_OK(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+      max_clusters[dev] = n > 0 ? n : 1;
+    }
+    attr_set[dev] = true;
+  }
+  const int units = TWO ? max_clusters[dev] : sm_count();
+  const int grid_units = (int)(tiles < units ? tiles : units);
+  cfg.gridDim = dim3(TWO ? 2 * grid_units : grid_units, 1, 1);
+  I8L_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, ma, mb, p));
   return I8L_OK;
+}
+
+static bool pair_mode_enabled() {  // development override: I8L_PAIR=0 forces one CTA per tile
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("I8L_PAIR");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
 }
 
 static int launch_gemm(bool block, const int8_t* a_q, const int8_t* b_q, GemmParams p, int64_t batch, int64_t M,
@@ -572,27 +699,33 @@ static int launch_gemm(bool block, const int8_t* a_q, const int8_t* b_q, GemmPar
   if (!a_q || !b_q || !p.c) return fail(I8L_ERR_ARG, "null pointer");
   if (!aligned16(a_q) || !aligned16(b_q) || !aligned16(p.c)) return fail(I8L_ERR_ALIGN, "a_q, b_q, c must be 16-byte aligned");
   if (int e = check_arch()) return e;
+  // CTA pairs (cta_group::2) need two 128-row blocks of the same batch per tile.  They pay off for the
+  // whole-K accumulation (half the B traffic per SM: +2.5 % sustained at the power cap); the per-K-block
+  // hand-off of the block-scaled kinds is slower across two CTAs (990 vs 1510 TOP/s), so those stay 1-CTA.
+  const bool two = !block && pair_mode_enabled() && (M % 256 == 0);
   CUtensorMap ma, mb;
   if (int e = make_map(&ma, a_q, batch * M, K, BM)) return e;
-  if (int e = make_map(&mb, b_q, p.b_batched ? batch * N : N, K, BN)) return e;
+  if (int e = make_map(&mb, b_q, p.b_batched ? batch * N : N, K, two ? BM : BN)) return e;
   p.m_blocks = (int)(batch * M / 128);
   p.mpb = (int)(M / 128);
   p.n_tiles = (int)((N + BN - 1) / BN);
   p.M = (int)M;
   p.N = (int)N;
   p.KB = (int)(K / 128);
-  // M-blocks per raster group: the group's A panel (raster x 128 x K bytes) should stay L2-resident
-  // while the CTAs sweep the N tiles (measured best: 32 blocks at K = 8192, flat for deeper K).
+  // M-units (128-row blocks, or 256-row pair blocks) per raster group: the group's A panel should stay
+  // L2-resident while the N tiles are swept (measured best: 4096 rows at K = 8192, flat for deeper K).
   {
     const int64_t fit = (32ll << 20) / (128 * K);
-    p.raster = (int)(fit < 8 ? 8 : (fit > 32 ? 32 : fit));
+    const int blocks = (int)(fit < 8 ? 8 : (fit > 32 ? 32 : fit));
+    p.raster = two ? blocks / 2 : blocks;
   }
-  const int64_t tiles = (int64_t)p.m_blocks * p.n_tiles;
-  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  if (!block) return launch_kind<K_ROWCOL>(ma, mb, p, grid, st);
-  const bool scalar_factor = !p.exact && !p.divide && !p.dump && p.b_kind != I8L_BSCALE_GROUP;
-  if (scalar_factor) return launch_kind<K_BLOCK_FAST>(ma, mb, p, grid, st);
-  return launch_kind<K_BLOCK_GEN>(ma, mb, p, grid, st);
+  const int64_t tiles = (int64_t)(two ? p.m_blocks / 2 : p.m_blocks) * p.n_tiles;
+  const bool scalar_factor = block && !p.exact && !p.divide && !p.dump && p.b_kind != I8L_BSCALE_GROUP;
+#define I8L_LAUNCH(KIND) (two ? launch_kind<KIND, true>(ma, mb, p, tiles, st) : launch_kind<KIND, false>(ma, mb, p, tiles, st))
+  if (!block) return I8L_LAUNCH(K_ROWCOL);
+  if (scalar_factor) return I8L_LAUNCH(K_BLOCK_FAST);
+  return I8L_LAUNCH(K_BLOCK_GEN);
+#undef I8L_LAUNCH
 }
 
 }  // namespace i8l
