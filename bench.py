@@ -34,6 +34,8 @@ WORKLOADS = {
     "c3": (16384, 4096, 11008, "llama2-7b up-proj M=16384 K=4096 N=11008 block_channel fwd+dX+dW"),
     "sq8192": (8192, 8192, 8192, "square 8192^3 block_channel fwd+dX+dW"),
     "c1": (512, 1024, 1024, "config-1 512x1024x1024 block_channel fwd+dX+dW"),
+    "c2": (8192, 4096, 4096, "config-2 double_channel forward M=8192 K=4096 N=4096 (full Hadamard, bias)"),
+    "c2sq8192": (8192, 8192, 8192, "double_channel forward 8192^3 (full Hadamard)"),
 }
 NOMINAL_INT8_TOPS = 4500.0  # B200 dense INT8 datasheet figure
 
@@ -225,6 +227,40 @@ def main():
     ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
     gemm_events = []
 
+    if args.workload.startswith("c2"):
+        # double_channel forward only (BASELINE config 2): one step = rotate+quantize X per token,
+        # rotate+quantize W per channel, whole-K int32 GEMM with the row x column epilogue.  Single GPU.
+        if world > 1:
+            raise SystemExit("the double_channel workloads are single-GPU")
+        from triton_int8_b200 import double_channel as DC
+        bias = (torch.randn(N, device=dev) * 0.01).to(torch.bfloat16)
+
+        def dc_step(rec=None):
+            aq, a_s = Kn.quant_row(x[None], L.QMODE_ROWRCP, L.HAD_FULL)
+            wq, w_s = Kn.quant_row(w, L.QMODE_ROWRCP, L.HAD_FULL)
+            if rec is not None: rec[0].record()
+            y = Kn.gemm_rowcol(aq, wq, a_s, w_s, bias, 1.0 / K)
+            if rec is not None: rec[1].record()
+            return y
+        for _ in range(max(args.warmup, 3)):
+            dc_step()
+        torch.cuda.synchronize()
+        recs = [(ev(), ev()) for _ in range(args.steps)]
+        t0, t1 = ev(), ev()
+        t0.record()
+        for r in recs:
+            dc_step(r)
+        t1.record(); torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1) / args.steps
+        tg = statistics.mean(a.elapsed_time(b) for a, b in recs)
+        print(json.dumps({
+            "metric": "double_channel_fwd_tokens_per_s", "value": M / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": desc, "M": M, "K": K, "N": N},
+            "gemm_ms": tg, "gemm_tops": 2.0 * M * N * K / tg / 1e9, "gpu_launches": 3 * args.steps}))
+        return
+
     def step(record=False):
         # forward
         xq, xs, xqt, xst = Kn.quant_tile(x[None], L.GRAN_TILE128, L.QMODE_TRITON, 0, natural=True, transposed=True)
@@ -281,6 +317,26 @@ def main():
     t_fwd, t_dx, t_dw = avg(0, 1), avg(2, 3), avg(4, 5)
     ops = 2.0 * M * Nl * K
     tops = {"fwd": ops / t_fwd / 1e9, "dx": ops / t_dx / 1e9, "dw": ops / t_dw / 1e9}
+    # quantizer bandwidth (HBM-bound kernels), timed alone
+    def time_fn(fn, n=5):
+        fn(); torch.cuda.synchronize()
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record(); torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+    tq = time_fn(lambda: Kn.quant_tile(dy[None], L.GRAN_TILE128, L.QMODE_TRITON, 0, natural=True, transposed=True))
+    tq1 = time_fn(lambda: Kn.quant_tile(dy[None], L.GRAN_TILE128, L.QMODE_TRITON, 0, natural=True, transposed=False))
+    tr_ = time_fn(lambda: Kn.quant_row(w, L.QMODE_TRITON, 0))
+    E = dy.numel()
+    quant = {
+        "tile128_dual_out_gbs": (2 * E + 2 * E) / tq / 1e6, "tile128_gbs": (2 * E + E) / tq1 / 1e6,
+        "row_gbs": 3 * w.numel() / tr_ / 1e6, "hbm_peak_gbs": measured_peaks()[0]["hbm_gbs"],
+        "tile128_dual_frac": (4 * E) / tq / 1e6 / measured_peaks()[0]["hbm_gbs"],
+        "tile128_frac": (3 * E) / tq1 / 1e6 / measured_peaks()[0]["hbm_gbs"],
+    }
+
     peaks, peak_src = measured_peaks()
     # INT8 tensor peak: MEASURED_PEAKS.json has no INT8 entry, so the cuBLAS int8 GEMM (torch._int_mm,
     # a library kernel used only as the measuring stick) is timed here on 8192^3: best single launch
@@ -324,25 +380,6 @@ def main():
         "peak_burst": int8_burst,
         "frac_of_nominal_4500": ops / t_gemm / 1e9 / NOMINAL_INT8_TOPS,
         "algorithmic_ops_per_launch": ops,
-    }
-
-    # quantizer bandwidth (HBM-bound kernels), timed alone
-    def time_fn(fn, n=5):
-        fn(); torch.cuda.synchronize()
-        a, b = ev(), ev()
-        a.record()
-        for _ in range(n):
-            fn()
-        b.record(); torch.cuda.synchronize()
-        return a.elapsed_time(b) / n
-    tq = time_fn(lambda: Kn.quant_tile(dy[None], L.GRAN_TILE128, L.QMODE_TRITON, 0, natural=True, transposed=True))
-    tq1 = time_fn(lambda: Kn.quant_tile(dy[None], L.GRAN_TILE128, L.QMODE_TRITON, 0, natural=True, transposed=False))
-    tr_ = time_fn(lambda: Kn.quant_row(w, L.QMODE_TRITON, 0))
-    E = dy.numel()
-    quant = {
-        "tile128_dual_out_gbs": (2 * E + 2 * E) / tq / 1e6, "tile128_gbs": (2 * E + E) / tq1 / 1e6,
-        "row_gbs": 3 * w.numel() / tr_ / 1e6, "hbm_peak_gbs": peaks["hbm_gbs"],
-        "tile128_frac": (3 * E) / tq1 / 1e6 / peaks["hbm_gbs"],
     }
 
     # end-to-end: host buffers in, results checksum out, through the public module API

@@ -62,7 +62,9 @@ extern "C" {
  *                  scale: TILE128 -> fp32 [batch, rows/128, cols/128]; GROUP128 -> [batch, rows, cols/128].
  *   qt / scale_t : the operand x^T (per batch), contraction axis = rows.  qt is int8 [batch, cols, rows].
  *                  scale_t: TILE128 -> [batch, cols/128, rows/128]; GROUP128 -> [batch, cols, rows/128].
- * Either pair may be NULL (not produced).  hadamard is I8L_HAD_NONE or I8L_HAD_128.
+ * Either pair may be NULL (not produced).  hadamard is I8L_HAD_NONE or I8L_HAD_128; the rotation
+ * always runs along the contraction axis of the operand it belongs to (cols for q, rows for qt), so
+ * with a rotation the two operands come from two passes over x instead of one.
  * Replaces triton_per_block_quant (triton/block_channel_fwd32.py:194-212,
  * triton/block_channel_bwd33.py:122-138) and, through qt, the transposed copies a linear layer's
  * dW = dY^T X needs.

@@ -376,5 +376,5 @@ def linear_block_channel(x, w, dy, hadamard128: bool = False, bias=None):
         y = y + bias.float()
     wt, dyt, xt = w.t().contiguous(), dy.t().contiguous(), x.t().contiguous()
     dx = block_channel_fwd_32(rot(dy)[None], rot(wt), return_fp32=True)[0] * post
-    dw = block_channel_bwd_33(rot(dyt)[None], rot(xt)[None], return_fp32=True)[0] * post
+    dw = block_channel_bwd_33(rot(dyt)[None], rot(xt)[None], return_fp32=True)[0] * post  # rotated along M
     return y.to(torch.bfloat16), dx.to(torch.bfloat16), dw.to(torch.bfloat16)

@@ -81,15 +81,15 @@ def test_config3_hadamard_block_channel_full_size():
     wt = w.t().contiguous().cpu()
     dx_ref = (R.block_channel_fwd_32(rot(dy[rb].cpu())[None], rot(wt), return_fp32=True)[0] / 128).to(torch.bfloat16)
     assert R.rel_fro(dx[rb].cpu().float(), dx_ref.float()) < TOL
-    # dW (not rotated): one 128-channel block x two 128-wide K blocks, contraction over all M
+    # dW (rotated along the tokens): one 128-channel block x two 128-wide K blocks, contraction over all M
     nb, kb = slice(128 * 3, 128 * 4), slice(128 * 5, 128 * 7)
-    dw_ref = R.block_channel_bwd_33(dy[:, nb].t().contiguous().cpu()[None], x[:, kb].t().contiguous().cpu()[None])[0]
+    dw_ref = (R.block_channel_bwd_33(rot(dy[:, nb].t().contiguous().cpu())[None], rot(x[:, kb].t().contiguous().cpu())[None],
+                                      return_fp32=True)[0] / 128).to(torch.bfloat16)
     assert R.rel_fro(dw[nb, kb].cpu().float(), dw_ref.float()) < TOL
     # all three against the exact products (the reference's own gate)
     assert R.calc_diff(y.float(), x.float() @ w.float().t()) < 1e-3
     assert R.calc_diff(dx.float(), dy.float() @ w.float()) < 1e-3
-    # dW is not rotated (its contraction axis is M): the heavy-tailed outliers of X cost accuracy there
-    assert R.calc_diff(dw.float(), dy.float().t() @ x.float()) < 2e-2
+    assert R.calc_diff(dw.float(), dy.float().t() @ x.float()) < 1e-3
 
 
 def test_config4_llama7b_layer_chain_full_tokens():

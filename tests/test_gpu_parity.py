@@ -258,3 +258,17 @@ def test_errors_are_reported_not_swallowed():
         BC.triton_per_block_quant(torch.zeros(1, 128, 128, dtype=torch.bfloat16))   # CPU tensor: no fallback
     with pytest.raises(TypeError):
         BC.triton_per_block_quant(torch.zeros(1, 128, 128, device=DEV))             # fp32 input
+
+
+@pytest.mark.parametrize("gran", ["tile", "group"])
+def test_hadamard_along_tokens_for_transposed_operand(gran):
+    """The dW operands are x^T rotated along the tokens (rows of x): bit-equal to the oracle applied to
+    the materialised transpose."""
+    g = torch.Generator().manual_seed(17)
+    x = (torch.randn(2, 256, 384, generator=g) * 2).to(torch.bfloat16)
+    x[0, 3, 5] = 60.0
+    G = L.GRAN_TILE128 if gran == "tile" else L.GRAN_GROUP128
+    _, _, qt, st = K.quant_tile(x.to(DEV), G, L.QMODE_TRITON, 128, natural=False, transposed=True)
+    xt_rot = R.hadamard(x.transpose(1, 2).contiguous(), 128)
+    q_ref, s_ref = R.quant_tile128(xt_rot) if gran == "tile" else R.quant_rowgroup128(xt_rot)
+    _same(qt, q_ref, "rotated transposed int8"); _same(st, s_ref, "rotated transposed scale")

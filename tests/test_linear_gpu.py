@@ -72,7 +72,8 @@ def test_linear_hadamard128_forward_and_dx():
     rot = lambda t: R.hadamard(t, 128)
     y_ref = (R.block_channel_fwd_32(rot(x)[None], rot(w), return_fp32=True)[0] / 128).to(torch.bfloat16)
     dx_ref = (R.block_channel_fwd_32(rot(dy)[None], rot(w.t().contiguous()), return_fp32=True)[0] / 128).to(torch.bfloat16)
-    dw_ref = R.block_channel_bwd_33(dy.t().contiguous()[None], x.t().contiguous()[None])[0]
+    dw_ref = (R.block_channel_bwd_33(rot(dy.t().contiguous())[None], rot(x.t().contiguous())[None],
+                                      return_fp32=True)[0] / 128).to(torch.bfloat16)
     assert R.rel_fro(y.cpu().float(), y_ref.float()) < TOL
     assert R.rel_fro(dx.cpu().float(), dx_ref.float()) < TOL
     assert R.rel_fro(dw.cpu().float(), dw_ref.float()) < TOL

@@ -220,6 +220,85 @@ quant_tile_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t col
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Transposed operand with the rotation along ITS contraction axis, i.e. along the rows of x: the dW
+// operands dY^T and X^T of a rotated linear layer (contraction over the tokens).  One CTA per 128x128
+// tile: the tile is staged in shared memory as fp32, thread (c, h) then owns rows 64h..64h+63 of
+// column c, runs six butterfly stages in registers and the last one with its partner lane, rounds to
+// bf16, and writes 64 consecutive bytes of output row c.
+// ------------------------------------------------------------------------------------------------
+template <int GRAN, int MODE>
+__global__ void __launch_bounds__(256)
+quant_tile_hadrows_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t cols,
+                          int8_t* __restrict__ qt, float* __restrict__ scale_t) {
+  extern __shared__ float s_tile[];  // [128][129]
+  __shared__ float s_red[8];
+  constexpr int LD = 129;
+  const int tid = threadIdx.x, w = tid >> 5, l = tid & 31, cc = l & 15, half = l >> 4;
+  const int64_t r_base = (int64_t)blockIdx.y * 128, c_base = (int64_t)blockIdx.x * 128;
+  const int64_t boff = (int64_t)blockIdx.z * rows * cols;
+  const __nv_bfloat16* xb = x + boff;
+#pragma unroll
+  for (int it = 0; it < 2; ++it)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = 16 * w + 8 * it + 4 * half + i;
+      float v[8];
+      unpack8(__ldg(reinterpret_cast<const uint4*>(xb + (r_base + r) * cols + c_base + 8 * cc)), v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s_tile[r * LD + 8 * cc + j] = v[j];
+    }
+  __syncthreads();
+  const int c = tid >> 1, h = tid & 1;
+  float v[64];
+#pragma unroll
+  for (int k = 0; k < 64; ++k) v[k] = s_tile[(64 * h + k) * LD + c];
+#pragma unroll
+  for (int span = 1; span < 64; span <<= 1) {
+#pragma unroll
+    for (int k = 0; k < 64; ++k) {
+      if ((k & span) == 0) {
+        const float a = v[k], b = v[k | span];
+        v[k] = __fadd_rn(a, b);
+        v[k | span] = __fsub_rn(a, b);
+      }
+    }
+  }
+  float m = 0.f;
+#pragma unroll
+  for (int k = 0; k < 64; ++k) {  // span 64: partner lane holds the other half of the column
+    const float o = __shfl_xor_sync(0xffffffffu, v[k], 1);
+    v[k] = round_to_bf16(h ? __fsub_rn(o, v[k]) : __fadd_rn(v[k], o));
+    m = fmaxf(m, fabsf(v[k]));
+  }
+  float s, stored;
+  if (GRAN == I8L_GRAN_TILE128) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (l == 0) s_red[w] = m;
+    __syncthreads();
+    m = s_red[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) m = fmaxf(m, s_red[k]);
+    make_scale<MODE>(m, s, stored);
+    if (tid == 0) scale_t[((int64_t)blockIdx.z * (cols / 128) + blockIdx.x) * (rows / 128) + blockIdx.y] = stored;
+  } else {  // one scale per output row (column of x) and 128 contraction elements
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    make_scale<MODE>(m, s, stored);
+    if (h == 0) scale_t[((int64_t)blockIdx.z * cols + c_base + c) * (rows / 128) + blockIdx.y] = stored;
+  }
+  int8_t* out = qt + boff + (c_base + c) * rows + r_base + 64 * h;
+#pragma unroll
+  for (int k = 0; k < 64; k += 16) {
+    uint4 o;
+    o.x = pack4(quant1<MODE>(v[k], s), quant1<MODE>(v[k + 1], s), quant1<MODE>(v[k + 2], s), quant1<MODE>(v[k + 3], s));
+    o.y = pack4(quant1<MODE>(v[k + 4], s), quant1<MODE>(v[k + 5], s), quant1<MODE>(v[k + 6], s), quant1<MODE>(v[k + 7], s));
+    o.z = pack4(quant1<MODE>(v[k + 8], s), quant1<MODE>(v[k + 9], s), quant1<MODE>(v[k + 10], s), quant1<MODE>(v[k + 11], s));
+    o.w = pack4(quant1<MODE>(v[k + 12], s), quant1<MODE>(v[k + 13], s), quant1<MODE>(v[k + 14], s), quant1<MODE>(v[k + 15], s));
+    *reinterpret_cast<uint4*>(out + k) = o;
+  }
+}
+
 // Column absmax of x [rows, cols] into colmax[cols] (pre-zeroed); |x| >= 0 so the float bit
 // patterns order like integers and atomicMax on int is exact.
 __global__ void __launch_bounds__(256)
@@ -402,9 +481,18 @@ template <int GRAN, int MODE>
 static int dispatch_tile(const void* x, int64_t batch, int64_t rows, int64_t cols, bool had, int8_t* q,
                          float* scale, int8_t* qt, float* scale_t, const float* colmax, cudaStream_t st) {
   const bool n = q != nullptr, t = qt != nullptr;
-  if (had) {
-    if (t) return fail(I8L_ERR_ARG, "Hadamard rotation with transposed output is not available in the tile kernel");
-    launch_tile<GRAN, MODE, true, true, false>(x, batch, rows, cols, q, scale, qt, scale_t, colmax, st);
+  if (had) {  // the two orientations rotate along different axes: one launch each
+    if (n) launch_tile<GRAN, MODE, true, true, false>(x, batch, rows, cols, q, scale, nullptr, nullptr, colmax, st);
+    if (t) {
+      constexpr size_t smem = 128 * 129 * sizeof(float);
+      static bool attr_done = false;
+      if (!attr_done) {
+        I8L_CUDA_OK(cudaFuncSetAttribute(quant_tile_hadrows_kernel<GRAN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_done = true;
+      }
+      dim3 grid((unsigned)(cols / 128), (unsigned)(rows / 128), (unsigned)batch);
+      quant_tile_hadrows_kernel<GRAN, MODE><<<grid, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(x), rows, cols, qt, scale_t);
+    }
   } else if (GRAN == I8L_GRAN_TILE128) {
     if (n && t) launch_tile<GRAN, MODE, false, true, true>(x, batch, rows, cols, q, scale, qt, scale_t, colmax, st);
     else if (n) launch_tile<GRAN, MODE, false, true, false>(x, batch, rows, cols, q, scale, qt, scale_t, colmax, st);

@@ -24,8 +24,9 @@ from . import kernels as K
 @dataclass(frozen=True)
 class Int8Config:
     """scaling: 'tile128' (reference block_channel) or 'row128' (one scale per row and 128
-    contraction elements); round: 'half_up' (reference) or 'rne'; hadamard: 0 or 128 (rotate the
-    operands of Y and dX in 128-wide groups along their contraction axis; dW is not rotated);
+    contraction elements); round: 'half_up' (reference) or 'rne'; hadamard: 0 or 128 (rotate both
+    operands of every GEMM in 128-wide groups along that GEMM's contraction axis: K for Y, N for dX,
+    the tokens for dW; each product is rescaled by 1/128);
     exact: reproduce the reference's fp32 operation order bit for bit (slower)."""
     scaling: str = "tile128"
     round: str = "half_up"
@@ -65,8 +66,8 @@ def linear_forward(x2: torch.Tensor, weight: torch.Tensor, bias, cfg: Int8Config
     operand for dW (or None when want_xt is False)."""
     fuse_t = want_xt and not cfg.hadamard
     xq, xs, xqt, xst = K.quant_tile(x2[None], cfg.gran, cfg.qmode, cfg.hadamard, natural=True, transposed=fuse_t)
-    if want_xt and not fuse_t:  # rotated forward operand, unrotated dW operand: second pass over X
-        _, _, xqt, xst = K.quant_tile(x2[None], cfg.gran, cfg.qmode, 0, natural=False, transposed=True)
+    if want_xt and not fuse_t:  # the dW operand X^T is rotated along the tokens, not along K: second pass over X
+        _, _, xqt, xst = K.quant_tile(x2[None], cfg.gran, cfg.qmode, cfg.hadamard, natural=False, transposed=True)
     wq, ws = K.quant_row(weight, cfg.qmode, cfg.hadamard)
     y = K.gemm_block(xq, wq, xs, ws, cfg.a_kind, L.BSCALE_CHANNEL, bias, cfg.post, cfg.flags)[0]
     return y, (xqt, xst)
@@ -79,7 +80,7 @@ def quantize_grad_output(dy2: torch.Tensor, cfg: Int8Config = DEFAULT, need_dx: 
     dyq, dys, dyqt, dyst = K.quant_tile(dy2[None], cfg.gran, cfg.qmode, cfg.hadamard,
                                         natural=need_dx, transposed=fuse_t)
     if need_dw and not fuse_t:
-        _, _, dyqt, dyst = K.quant_tile(dy2[None], cfg.gran, cfg.qmode, 0, natural=False, transposed=True)
+        _, _, dyqt, dyst = K.quant_tile(dy2[None], cfg.gran, cfg.qmode, cfg.hadamard, natural=False, transposed=True)
     return (dyq, dys), (dyqt, dyst)
 
 
@@ -96,7 +97,7 @@ def grad_input(dy_op, weight: torch.Tensor, cfg: Int8Config = DEFAULT) -> torch.
 def grad_weight(dyt_op, saved_xt, cfg: Int8Config = DEFAULT) -> torch.Tensor:
     """dW = dY^T X, bf16 [N, K], both operands scaled in groups along M."""
     (dyqt, dyst), (xqt, xst) = dyt_op, saved_xt
-    return K.gemm_block(dyqt, xqt, dyst, xst, cfg.a_kind, cfg.bt_kind, None, 1.0, cfg.flags)[0]
+    return K.gemm_block(dyqt, xqt, dyst, xst, cfg.a_kind, cfg.bt_kind, None, cfg.post, cfg.flags)[0]
 
 
 def linear_backward(dy2: torch.Tensor, weight: torch.Tensor, saved_xt, cfg: Int8Config = DEFAULT,
