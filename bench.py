@@ -121,9 +121,11 @@ class CpuReference:
     is timed on the first `sample` tokens.  Whole-workload throughput is extrapolated linearly in the
     token count:  tokens/s = M / (t_weight + t_tokens * M / sample)."""
 
-    def __init__(self, M, K, N, sample):
+    def __init__(self, M, K, N, sample, had=0):
         from oracle import ref_semantics as R
         self.R, self.M, self.K, self.N, self.Ms = R, M, K, N, sample
+        self.rot = (lambda t: R.hadamard(t, 128)) if had else (lambda t: t)
+        self.had = had
         self.cores = os.cpu_count() or 1
         torch.set_num_threads(self.cores)
         g = torch.Generator().manual_seed(20260004)
@@ -134,20 +136,21 @@ class CpuReference:
         self.w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
         self.dy = (torch.randn(sample, N, generator=g) * 1e-3).to(torch.bfloat16)
         t0 = time.perf_counter()
-        self.wq, self.ws = R.quant_token(self.w)
-        self.wtq, self.wts = R.quant_token(self.w.t().contiguous())
+        self.wq, self.ws = R.quant_token(self.rot(self.w))
+        self.wtq, self.wts = R.quant_token(self.rot(self.w.t().contiguous()))
         self.t_weight = time.perf_counter() - t0
 
     def tokens_step(self):
         R = self.R
         t0 = time.perf_counter()
-        xq, xs = R.quant_tile128(self.x[None])
-        y = R.gemm_block_fwd(xq, self.wq, xs, self.ws).to(torch.bfloat16)
-        dyq, dys = R.quant_tile128(self.dy[None])
-        dx = R.gemm_block_fwd(dyq, self.wtq, dys, self.wts).to(torch.bfloat16)
-        dytq, dyts = R.quant_tile128(self.dy.t().contiguous()[None], clamp=False)
-        xtq, xts = R.quant_tile128(self.x.t().contiguous()[None], clamp=False)
-        dw = R.gemm_block_bwd(dytq, xtq, dyts, xts).to(torch.bfloat16)
+        rot, post = self.rot, (1.0 / 128 if self.had else 1.0)
+        xq, xs = R.quant_tile128(rot(self.x)[None])
+        y = (R.gemm_block_fwd(xq, self.wq, xs, self.ws) * post).to(torch.bfloat16)
+        dyq, dys = R.quant_tile128(rot(self.dy)[None])
+        dx = (R.gemm_block_fwd(dyq, self.wtq, dys, self.wts) * post).to(torch.bfloat16)
+        dytq, dyts = R.quant_tile128(rot(self.dy.t().contiguous())[None], clamp=False)
+        xtq, xts = R.quant_tile128(rot(self.x.t().contiguous())[None], clamp=False)
+        dw = (R.gemm_block_bwd(dytq, xtq, dyts, xts) * post).to(torch.bfloat16)
         del y, dx, dw
         return time.perf_counter() - t0
 
@@ -159,11 +162,11 @@ class CpuReference:
                 f"[{self.N},{self.K}] once; extrapolated linearly in tokens")
 
 
-def run_reference_arm(args, M, K, N, desc):
+def run_reference_arm(args, M, K, N, desc, had):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    ref = CpuReference(M, K, N, min(M, 512))
+    ref = CpuReference(M, K, N, min(M, 512), had)
     for _ in range(min(args.warmup, 1)):
         ref.tokens_step()
     n = max(1, min(args.steps, 5))
@@ -187,13 +190,19 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
+    ap.add_argument("--hadamard", type=int, default=None, choices=[0, 128],
+                    help="128-point rotation in front of every quantizer (default: 128 for c3 and c5, as BASELINE.json "
+                         "describes those configurations; 0 otherwise)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     M, K, N, desc = WORKLOADS[args.workload]
+    had = args.hadamard if args.hadamard is not None else (128 if args.workload in ("c3", "c5") else 0)
+    if had:
+        desc += ", 128-point Hadamard rotation along each GEMM's contraction axis"
 
     if args.impl == "reference":
-        run_reference_arm(args, M, K, N, desc)
+        run_reference_arm(args, M, K, N, desc, had)
         return
 
     if not torch.cuda.is_available():
@@ -261,19 +270,26 @@ def main():
             "gemm_ms": tg, "gemm_tops": 2.0 * M * N * K / tg / 1e9, "gpu_launches": 3 * args.steps}))
         return
 
+    from triton_int8_b200.linear import Int8Config
+    cfg = Int8Config(hadamard=had)
+    launches_per_step = 10 if had else 8
+
     def step(record=False):
         # forward
-        xq, xs, xqt, xst = Kn.quant_tile(x[None], L.GRAN_TILE128, L.QMODE_TRITON, 0, natural=True, transposed=True)
-        wq, ws = Kn.quant_row(w, L.QMODE_TRITON, 0)
+        _, saved_xt_unused = None, None
+        xq, xs, xqt, xst = Kn.quant_tile(x[None], cfg.gran, cfg.qmode, had, natural=True, transposed=not had)
+        if had:   # the dW operand X^T is rotated along the tokens: its own pass
+            _, _, xqt, xst = Kn.quant_tile(x[None], cfg.gran, cfg.qmode, had, natural=False, transposed=True)
+        wq, ws = Kn.quant_row(w, cfg.qmode, had)
         e = [ev() for _ in range(6)] if record else None
         if record: e[0].record()
-        y = Kn.gemm_block(xq, wq, xs, ws, L.ASCALE_TILE, L.BSCALE_CHANNEL)
+        y = Kn.gemm_block(xq, wq, xs, ws, L.ASCALE_TILE, L.BSCALE_CHANNEL, None, cfg.post)
         if record: e[1].record()
         # backward
-        dy_op, dyt_op = quantize_grad_output(dy, DEFAULT, True, True)
-        wtq, wts = Kn.quant_col_t(w, L.QMODE_TRITON)
+        dy_op, dyt_op = quantize_grad_output(dy, cfg, True, True)
+        wtq, wts = Kn.quant_col_t(w, cfg.qmode, had)
         if record: e[2].record()
-        dx_partial = Kn.gemm_block(dy_op[0], wtq, dy_op[1], wts, L.ASCALE_TILE, L.BSCALE_CHANNEL)[0]
+        dx_partial = Kn.gemm_block(dy_op[0], wtq, dy_op[1], wts, L.ASCALE_TILE, L.BSCALE_CHANNEL, None, cfg.post)[0]
         if record: e[3].record()
         if world > 1:
             main = torch.cuda.current_stream()
@@ -284,7 +300,7 @@ def main():
         else:
             dx = dx_partial
         if record: e[4].record()
-        dw = grad_weight(dyt_op, (xqt, xst), DEFAULT)
+        dw = grad_weight(dyt_op, (xqt, xst), cfg)
         if record: e[5].record()
         if world > 1:
             torch.cuda.current_stream().wait_stream(step_obj.comm_stream)
@@ -329,8 +345,11 @@ def main():
     tq = time_fn(lambda: Kn.quant_tile(dy[None], L.GRAN_TILE128, L.QMODE_TRITON, 0, natural=True, transposed=True))
     tq1 = time_fn(lambda: Kn.quant_tile(dy[None], L.GRAN_TILE128, L.QMODE_TRITON, 0, natural=True, transposed=False))
     tr_ = time_fn(lambda: Kn.quant_row(w, L.QMODE_TRITON, 0))
+    th = time_fn(lambda: Kn.quant_tile(dy[None], L.GRAN_TILE128, L.QMODE_TRITON, 128, natural=True, transposed=False))
+    tht = time_fn(lambda: Kn.quant_tile(dy[None], L.GRAN_TILE128, L.QMODE_TRITON, 128, natural=False, transposed=True))
     E = dy.numel()
     quant = {
+        "tile128_had128_gbs": 3 * E / th / 1e6, "tile128_had128_transposed_gbs": 3 * E / tht / 1e6,
         "tile128_dual_out_gbs": (2 * E + 2 * E) / tq / 1e6, "tile128_gbs": (2 * E + E) / tq1 / 1e6,
         "row_gbs": 3 * w.numel() / tr_ / 1e6, "hbm_peak_gbs": measured_peaks()[0]["hbm_gbs"],
         "tile128_dual_frac": (4 * E) / tq / 1e6 / measured_peaks()[0]["hbm_gbs"],
@@ -388,7 +407,7 @@ def main():
         from triton_int8_b200.linear import Int8Linear
         xh = x.cpu().pin_memory()
         dyh = dy.cpu().pin_memory()
-        lin = Int8Linear(K, Nl, bias=False, device=dev)
+        lin = Int8Linear(K, Nl, bias=False, device=dev, config=cfg)
         with torch.no_grad():
             lin.weight.copy_(w)
         res_h = torch.empty(3, dtype=torch.float32).pin_memory()
@@ -427,7 +446,7 @@ def main():
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        ref = CpuReference(M, K, N, min(M, 512))
+        ref = CpuReference(M, K, N, min(M, 512), had)
         t_tok = statistics.median([ref.tokens_step() for _ in range(3)])
         cpu_baseline = {"value": ref.tokens_per_s(t_tok), "unit": "tokens/s", "cores": ref.cores, "kind": "port",
                         "sample": ref.describe(3), "t_weight_s": ref.t_weight, "t_tokens_s": t_tok}
@@ -437,11 +456,11 @@ def main():
             "metric": "linear_fwd_bwd_tokens_per_s", "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": desc, "M": M, "K": K, "N": N, "N_per_gpu": Nl, "parallelism": f"tp{world}-column",
+            "config": {"workload": desc, "hadamard": had, "M": M, "K": K, "N": N, "N_per_gpu": Nl, "parallelism": f"tp{world}-column",
                        "l2": "inputs (X 0.5 GB + dY >= 0.2 GB per step) exceed the 126 MB L2; no explicit flush"},
             "tops_per_gpu": tops, "gemm_ms": {"fwd": t_fwd, "dx": t_dx, "dw": t_dw},
             "roofline": roofline, "quantizers": quant, "cpu_baseline": cpu_baseline, "e2e": e2e,
-            "gpu_launches": 8 * args.steps, "clocks": clk.summary(),
+            "gpu_launches": launches_per_step * args.steps, "clocks": clk.summary(),
         }))
     if world > 1:
         dist.destroy_process_group()

@@ -93,6 +93,15 @@ I8L_API int i8l_quant_col_t(const void* x, int64_t rows, int64_t cols, int qmode
                     float* colmax_scratch, void* stream);
 
 /*
+ * As i8l_quant_col_t, with a 128-point Walsh-Hadamard rotation along the rows of x (the contraction
+ * axis of the transposed operand) in front: W^T of a rotated linear layer's dX GEMM.  Two passes over
+ * x (column absmax of the rotated values, then quantise); qmode TRITON or RNE.
+ * No counterpart in the reference.
+ */
+I8L_API int i8l_quant_col_t_rot(const void* x, int64_t rows, int64_t cols, int qmode, int8_t* qt,
+                                float* scale_t, float* colmax_scratch, void* stream);
+
+/*
  * Same result as i8l_quant_col_t, for callers that cannot hand over scratch memory: code running
  * where device allocation is off limits (inside a framework's memory-pool callback or a stream
  * capture section, in a plugin sandbox that forbids cudaMalloc, or late in a job when the pool is

@@ -106,6 +106,9 @@ def test_quant_row_modes_and_col_t():
     qt, st = K.quant_col_t(w.to(DEV), L.QMODE_TRITON)          # W^T per input channel, for dX
     q_ref, s_ref = R.quant_token(w.t().contiguous())
     _same(qt, q_ref, "col_t int8"); _same(st, s_ref.view(-1), "col_t scale")
+    qt, st = K.quant_col_t(w.to(DEV), L.QMODE_TRITON, hadamard=128)   # rotated along the rows of w (N)
+    q_ref, s_ref = R.quant_token(R.hadamard(w.t().contiguous(), 128))
+    _same(qt, q_ref, "rotated col_t int8"); _same(st, s_ref.view(-1), "rotated col_t scale")
 
 
 @pytest.mark.parametrize("kind", ["tile128", "row128", "rowfull"])

@@ -39,6 +39,7 @@ int check_arch() {
 // 16-byte vector and 16 lanes cover one 256-byte row segment.
 // ------------------------------------------------------------------------------------------------
 constexpr int GRAN_COLFULL = 3;  // internal: per-column scale from a precomputed column absmax
+constexpr int GRAN_COLMAX_PASS = 4;  // internal: only accumulate the column absmax of the rotated tile
 
 __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
   return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) |
@@ -230,7 +231,7 @@ quant_tile_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t col
 template <int GRAN, int MODE>
 __global__ void __launch_bounds__(256)
 quant_tile_hadrows_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t cols,
-                          int8_t* __restrict__ qt, float* __restrict__ scale_t) {
+                          int8_t* __restrict__ qt, float* __restrict__ scale_t, float* __restrict__ colmax) {
   extern __shared__ float s_tile[];  // [128][129]
   __shared__ float s_red[8];
   constexpr int LD = 129;
@@ -282,6 +283,13 @@ quant_tile_hadrows_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int
     for (int k = 1; k < 8; ++k) m = fmaxf(m, s_red[k]);
     make_scale<MODE>(m, s, stored);
     if (tid == 0) scale_t[((int64_t)blockIdx.z * (cols / 128) + blockIdx.x) * (rows / 128) + blockIdx.y] = stored;
+  } else if (GRAN == GRAN_COLMAX_PASS) {  // first pass of the whole-column scale: absmax of the rotated column
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    if (h == 0) atomicMax(reinterpret_cast<int*>(colmax + c_base + c), __float_as_int(m));
+    return;
+  } else if (GRAN == GRAN_COLFULL) {      // second pass: one scale per output row over all of its elements
+    make_scale<MODE>(colmax[c_base + c], s, stored);
+    if (h == 0 && blockIdx.y == 0) scale_t[c_base + c] = stored;
   } else {  // one scale per output row (column of x) and 128 contraction elements
     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
     make_scale<MODE>(m, s, stored);
@@ -491,7 +499,7 @@ static int dispatch_tile(const void* x, int64_t batch, int64_t rows, int64_t col
         attr_done = true;
       }
       dim3 grid((unsigned)(cols / 128), (unsigned)(rows / 128), (unsigned)batch);
-      quant_tile_hadrows_kernel<GRAN, MODE><<<grid, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(x), rows, cols, qt, scale_t);
+      quant_tile_hadrows_kernel<GRAN, MODE><<<grid, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(x), rows, cols, qt, scale_t, nullptr);
     }
   } else if (GRAN == I8L_GRAN_TILE128) {
     if (n && t) launch_tile<GRAN, MODE, false, true, true>(x, batch, rows, cols, q, scale, qt, scale_t, colmax, st);
@@ -600,6 +608,39 @@ extern "C" int i8l_quant_col_t(const void* x, int64_t rows, int64_t cols, int qm
   I8L_COL_CASE(I8L_QMODE_ROWRCP)
 #undef I8L_COL_CASE
   return fail(I8L_ERR_ARG, "i8l_quant_col_t: unsupported qmode=%d", qmode);
+}
+
+template <int MODE>
+static int launch_col_t_rot(const void* x, int64_t rows, int64_t cols, int8_t* qt, float* scale_t, float* colmax,
+                            cudaStream_t st) {
+  constexpr size_t smem = 128 * 129 * sizeof(float);
+  static bool attr_done = false;
+  if (!attr_done) {
+    I8L_CUDA_OK(cudaFuncSetAttribute(quant_tile_hadrows_kernel<GRAN_COLMAX_PASS, MODE>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    I8L_CUDA_OK(cudaFuncSetAttribute(quant_tile_hadrows_kernel<GRAN_COLFULL, MODE>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_done = true;
+  }
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  dim3 grid((unsigned)(cols / 128), (unsigned)(rows / 128), 1);
+  quant_tile_hadrows_kernel<GRAN_COLMAX_PASS, MODE><<<grid, 256, smem, st>>>(xp, rows, cols, nullptr, nullptr, colmax);
+  quant_tile_hadrows_kernel<GRAN_COLFULL, MODE><<<grid, 256, smem, st>>>(xp, rows, cols, qt, scale_t, colmax);
+  I8L_CUDA_OK(cudaGetLastError());
+  return I8L_OK;
+}
+
+extern "C" int i8l_quant_col_t_rot(const void* x, int64_t rows, int64_t cols, int qmode, int8_t* qt, float* scale_t,
+                                   float* colmax_scratch, void* stream) {
+  if (int e = check_dims(1, rows, cols)) return e;
+  if (!x || !qt || !scale_t || !colmax_scratch) return fail(I8L_ERR_ARG, "null pointer");
+  if (!aligned16(x) || !aligned16(qt)) return fail(I8L_ERR_ALIGN, "x, qt must be 16-byte aligned");
+  if (int e = check_arch()) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  I8L_CUDA_OK(cudaMemsetAsync(colmax_scratch, 0, (size_t)cols * sizeof(float), st));
+  if (qmode == I8L_QMODE_TRITON) return launch_col_t_rot<I8L_QMODE_TRITON>(x, rows, cols, qt, scale_t, colmax_scratch, st);
+  if (qmode == I8L_QMODE_RNE) return launch_col_t_rot<I8L_QMODE_RNE>(x, rows, cols, qt, scale_t, colmax_scratch, st);
+  return fail(I8L_ERR_ARG, "i8l_quant_col_t_rot: unsupported qmode=%d", qmode);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -53,14 +53,18 @@ def quant_row(x: torch.Tensor, qmode: int = L.QMODE_TRITON, hadamard: int = 0):
     return q, s
 
 
-def quant_col_t(x: torch.Tensor, qmode: int = L.QMODE_TRITON):
-    """x bf16 [R, C] -> int8 x^T [C, R] with one scale per column of x, fp32 [C]."""
+def quant_col_t(x: torch.Tensor, qmode: int = L.QMODE_TRITON, hadamard: int = 0):
+    """x bf16 [R, C] -> int8 x^T [C, R] with one scale per column of x, fp32 [C]; hadamard=128 rotates
+    x^T in 128-wide groups along its contraction axis (the rows of x) first."""
     x = _check_bf16(x, "x")
     R, C = x.shape
     qt = torch.empty((C, R), dtype=torch.int8, device=x.device)
     st = torch.empty((C,), dtype=torch.float32, device=x.device)
     scratch = torch.empty((C,), dtype=torch.float32, device=x.device)
-    L.call("i8l_quant_col_t", x.data_ptr(), R, C, qmode, qt.data_ptr(), st.data_ptr(), scratch.data_ptr(), _stream())
+    if hadamard not in (0, 128):
+        raise ValueError("quant_col_t: hadamard must be 0 or 128")
+    L.call("i8l_quant_col_t_rot" if hadamard else "i8l_quant_col_t", x.data_ptr(), R, C, qmode, qt.data_ptr(),
+           st.data_ptr(), scratch.data_ptr(), _stream())
     return qt, st
 
 

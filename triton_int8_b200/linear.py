@@ -87,10 +87,7 @@ def quantize_grad_output(dy2: torch.Tensor, cfg: Int8Config = DEFAULT, need_dx: 
 def grad_input(dy_op, weight: torch.Tensor, cfg: Int8Config = DEFAULT) -> torch.Tensor:
     """dX = dY W, bf16 [M, K]; W^T is quantised per input channel."""
     dyq, dys = dy_op
-    if cfg.hadamard:   # rotation of W^T along N needs the transposed rows: weight-sized bf16 transpose
-        wtq, wts = K.quant_row(weight.t().contiguous(), cfg.qmode, cfg.hadamard)
-    else:
-        wtq, wts = K.quant_col_t(weight, cfg.qmode)
+    wtq, wts = K.quant_col_t(weight, cfg.qmode, cfg.hadamard)   # rotated along N when hadamard is on
     return K.gemm_block(dyq, wtq, dys, wts, cfg.a_kind, L.BSCALE_CHANNEL, None, cfg.post, cfg.flags)[0]
 
 
