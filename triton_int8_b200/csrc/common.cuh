@@ -48,16 +48,29 @@ __device__ __forceinline__ void make_scale(float amax, float& s, float& stored) 
   }
 }
 
+// One value: y = x*s, then floor(y + 0.5) clamped to [-128, 127] (a single saturating
+// round-toward-minus-infinity conversion), or rint(y) clamped to [-127, 127] for the RNE mode.
 template <int MODE>
 __device__ __forceinline__ int quant1(float v, float s) {
-  float y = __fmul_rn(v, s);
+  const float y = __fmul_rn(v, s);
+  int q;
   if (MODE == I8L_QMODE_RNE) {
-    y = fminf(fmaxf(rintf(y), -127.0f), 127.0f);
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(y));
+    q = max(q, -127);
   } else {
-    y = floorf(__fadd_rn(y, 0.5f));
-    y = fminf(fmaxf(y, -128.0f), 127.0f);  // never active for FUSED: |x*s| < 127
+    asm("cvt.rmi.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(__fadd_rn(y, 0.5f)));  // never saturates for FUSED: |x*s| < 127
   }
-  return __float2int_rn(y);
+  return q;
+}
+
+// Four quantised values (sign-extended in 32-bit registers) -> four bytes, lowest address first.
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+  // cvt.pack puts its first operand in bits 8-15, the second in bits 0-7, and the low half of the
+  // third operand in bits 16-31
+  uint32_t hi, r;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(d), "r"(c));            // c | d<<8
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(a), "r"(hi));   // a | b<<8 | c<<16 | d<<24
+  return r;
 }
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t b) { return __uint_as_float(b << 16); }

@@ -41,11 +41,6 @@ int check_arch() {
 constexpr int GRAN_COLFULL = 3;  // internal: per-column scale from a precomputed column absmax
 constexpr int GRAN_COLMAX_PASS = 4;  // internal: only accumulate the column absmax of the rotated tile
 
-__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
-  return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) |
-         ((uint32_t)(d & 0xff) << 24);
-}
-
 // |x| maximum of the 8 bf16 values of a 16-byte vector, as two packed maxima (exact: bf16 compare).
 __device__ __forceinline__ __nv_bfloat162 absmax8(const uint4& u, __nv_bfloat162 m) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
@@ -222,6 +217,114 @@ quant_tile_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t col
 }
 
 // ------------------------------------------------------------------------------------------------
+// Natural operand with the 128-point rotation along the columns (its contraction axis).  Four lanes
+// share a row: lane j of the quad holds the 16-byte pieces 4c+j (c = 0..3) of the row's 128 values,
+// so each load instruction of a quad covers 64 contiguous bytes and only two of the seven butterfly
+// stages cross lanes (spans 8 and 16); spans 1-4 and 32-64 run in registers.
+// ------------------------------------------------------------------------------------------------
+template <int GRAN, int MODE>
+__global__ void __launch_bounds__(256, 3)
+quant_tile_hadcols_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t cols,
+                          int8_t* __restrict__ q, float* __restrict__ scale) {
+  __shared__ float s_red[8];
+  const int tid = threadIdx.x, w = tid >> 5, l = tid & 31, j4 = l & 3, rq = l >> 2;
+  const int64_t r_base = (int64_t)blockIdx.y * 128, c_base = (int64_t)blockIdx.x * 128;
+  const int64_t boff = (int64_t)blockIdx.z * rows * cols;
+  float s_tile = 0.f, s_row[2];
+  uint4 packed[2][4];  // rotated values, rounded to bf16
+  float tmax = 0.f;
+#pragma unroll
+  for (int it = 0; it < 2; ++it) {
+    const int r = 16 * w + 8 * it + rq;
+    const __nv_bfloat16* xr = x + boff + (r_base + r) * cols + c_base;
+    float v[4][8];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) unpack8(__ldg(reinterpret_cast<const uint4*>(xr + 8 * (4 * c + j4))), v[c]);
+    // spans 1, 2, 4: inside a piece
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+      for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+          if ((t & h) == 0) {
+            const float a = v[c][t], b = v[c][t | h];
+            v[c][t] = __fadd_rn(a, b);
+            v[c][t | h] = __fsub_rn(a, b);
+          }
+    // spans 8, 16: across the quad (element index = 32c + 8j + t)
+#pragma unroll
+    for (int m = 1; m < 4; m <<= 1) {
+      const bool upper = (j4 & m) != 0;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          const float o = __shfl_xor_sync(0xffffffffu, v[c][t], m);
+          v[c][t] = upper ? __fsub_rn(o, v[c][t]) : __fadd_rn(v[c][t], o);
+        }
+    }
+    // spans 32, 64: across the four pieces of the lane
+#pragma unroll
+    for (int h = 1; h < 4; h <<= 1)
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if ((c & h) == 0)
+#pragma unroll
+          for (int t = 0; t < 8; ++t) {
+            const float a = v[c][t], b = v[c | h][t];
+            v[c][t] = __fadd_rn(a, b);
+            v[c | h][t] = __fsub_rn(a, b);
+          }
+    float m = 0.f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed[it][c]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        h2[k] = __floats2bfloat162_rn(v[c][2 * k], v[c][2 * k + 1]);
+        m = fmaxf(m, fmaxf(fabsf(__low2float(h2[k])), fabsf(__high2float(h2[k]))));
+      }
+    }
+    if (GRAN == I8L_GRAN_GROUP128) {
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+      float stored;
+      make_scale<MODE>(m, s_row[it], stored);
+      if (j4 == 0) scale[((int64_t)blockIdx.z * rows + r_base + r) * (cols / 128) + blockIdx.x] = stored;
+    }
+    tmax = fmaxf(tmax, m);
+  }
+  if (GRAN == I8L_GRAN_TILE128) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+    if (l == 0) s_red[w] = tmax;
+    __syncthreads();
+    tmax = s_red[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) tmax = fmaxf(tmax, s_red[k]);
+    float stored;
+    make_scale<MODE>(tmax, s_tile, stored);
+    if (tid == 0) scale[((int64_t)blockIdx.z * (rows / 128) + blockIdx.y) * (cols / 128) + blockIdx.x] = stored;
+  }
+#pragma unroll
+  for (int it = 0; it < 2; ++it) {
+    const int r = 16 * w + 8 * it + rq;
+    const float s = GRAN == I8L_GRAN_TILE128 ? s_tile : s_row[it];
+    int8_t* qr = q + boff + (r_base + r) * cols + c_base;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      float v[8];
+      unpack8(packed[it][c], v);
+      uint2 o;
+      o.x = pack4(quant1<MODE>(v[0], s), quant1<MODE>(v[1], s), quant1<MODE>(v[2], s), quant1<MODE>(v[3], s));
+      o.y = pack4(quant1<MODE>(v[4], s), quant1<MODE>(v[5], s), quant1<MODE>(v[6], s), quant1<MODE>(v[7], s));
+      *reinterpret_cast<uint2*>(qr + 8 * (4 * c + j4)) = o;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // Transposed operand with the rotation along ITS contraction axis, i.e. along the rows of x: the dW
 // operands dY^T and X^T of a rotated linear layer (contraction over the tokens).  One CTA per 128x128
 // tile: the tile is staged in shared memory as fp32, thread (c, h) then owns rows 64h..64h+63 of
@@ -232,9 +335,9 @@ template <int GRAN, int MODE>
 __global__ void __launch_bounds__(256)
 quant_tile_hadrows_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t cols,
                           int8_t* __restrict__ qt, float* __restrict__ scale_t, float* __restrict__ colmax) {
-  extern __shared__ float s_tile[];  // [128][129]
+  extern __shared__ float s_tile[];  // [128][132]: rows 16-byte aligned for vector stores
   __shared__ float s_red[8];
-  constexpr int LD = 129;
+  constexpr int LD = 132;
   const int tid = threadIdx.x, w = tid >> 5, l = tid & 31, cc = l & 15, half = l >> 4;
   const int64_t r_base = (int64_t)blockIdx.y * 128, c_base = (int64_t)blockIdx.x * 128;
   const int64_t boff = (int64_t)blockIdx.z * rows * cols;
@@ -246,8 +349,8 @@ quant_tile_hadrows_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int
       const int r = 16 * w + 8 * it + 4 * half + i;
       float v[8];
       unpack8(__ldg(reinterpret_cast<const uint4*>(xb + (r_base + r) * cols + c_base + 8 * cc)), v);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) s_tile[r * LD + 8 * cc + j] = v[j];
+      *reinterpret_cast<float4*>(s_tile + r * LD + 8 * cc) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(s_tile + r * LD + 8 * cc + 4) = make_float4(v[4], v[5], v[6], v[7]);
     }
   __syncthreads();
   const int c = tid >> 1, h = tid & 1;
@@ -490,9 +593,12 @@ static int dispatch_tile(const void* x, int64_t batch, int64_t rows, int64_t col
                          float* scale, int8_t* qt, float* scale_t, const float* colmax, cudaStream_t st) {
   const bool n = q != nullptr, t = qt != nullptr;
   if (had) {  // the two orientations rotate along different axes: one launch each
-    if (n) launch_tile<GRAN, MODE, true, true, false>(x, batch, rows, cols, q, scale, nullptr, nullptr, colmax, st);
+    if (n) {
+      dim3 grid((unsigned)(cols / 128), (unsigned)(rows / 128), (unsigned)batch);
+      quant_tile_hadcols_kernel<GRAN, MODE><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows, cols, q, scale);
+    }
     if (t) {
-      constexpr size_t smem = 128 * 129 * sizeof(float);
+      constexpr size_t smem = 128 * 132 * sizeof(float);
       static bool attr_done = false;
       if (!attr_done) {
         I8L_CUDA_OK(cudaFuncSetAttribute(quant_tile_hadrows_kernel<GRAN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -613,7 +719,7 @@ extern "C" int i8l_quant_col_t(const void* x, int64_t rows, int64_t cols, int qm
 template <int MODE>
 static int launch_col_t_rot(const void* x, int64_t rows, int64_t cols, int8_t* qt, float* scale_t, float* colmax,
                             cudaStream_t st) {
-  constexpr size_t smem = 128 * 129 * sizeof(float);
+  constexpr size_t smem = 128 * 132 * sizeof(float);
   static bool attr_done = false;
   if (!attr_done) {
     I8L_CUDA_OK(cudaFuncSetAttribute(quant_tile_hadrows_kernel<GRAN_COLMAX_PASS, MODE>,
