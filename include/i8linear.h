@@ -130,7 +130,9 @@ I8L_API int i8l_quant_col_t_static(const void* x, int64_t rows, int64_t cols, in
 #define I8L_GEMM_EXACT_ORDER 1 /* per K step evaluate (float(P)*a_s)*b_s then add, unfused: bit-equal to the
                                   reference's fp32 result.  Without it the K-invariant factor is applied once
                                   at the end and multiply-adds are fused (same int32 partials). */
-#define I8L_GEMM_DIVIDE 2      /* scales are multipliers s: acc += float(P) / (a_s*b_s)  (fused variants) */
+#define I8L_GEMM_DIVIDE 2      /* scales are multipliers s: acc += float(P) / (a_s*b_s)  (fused variants); together with
+                                  EXACT_ORDER a true division per element, otherwise a multiplication by the rounded
+                                  reciprocal of a_s*b_s (differs from the division by at most 1 ulp per K block) */
 #define I8L_GEMM_OUT_F32 4     /* C is fp32 instead of bf16 */
 
 /*

@@ -220,9 +220,14 @@ def test_double_channel_matches_reference_kernels(golden_dir):
 def test_fused_matches_reference_kernels(golden_dir):
     g = _golden(golden_dir, "fused_small")
     a, w, b3 = make_inputs("small")
-    _same(FU.fused_int8_gemm(a.to(DEV), w.to(DEV), out_dtype=torch.float32), g["c_fwd"], "fused fwd fp32")
-    _same(FU.fused_int8_gemm(a.to(DEV), b3.to(DEV), out_dtype=torch.float32), g["c_bwd"], "fused bwd fp32")
-    _same(FU.fwd_32(a.to(DEV), w.to(DEV)), torch.as_tensor(g["c_fwd"]).to(torch.bfloat16))
+    _same(FU.fused_int8_gemm(a.to(DEV), w.to(DEV), out_dtype=torch.float32, exact=True), g["c_fwd"], "fused fwd fp32")
+    _same(FU.fused_int8_gemm(a.to(DEV), b3.to(DEV), out_dtype=torch.float32, exact=True), g["c_bwd"], "fused bwd fp32")
+    # default (fast) path: reciprocal instead of division, fused accumulation
+    for got, ref in ((FU.fused_int8_gemm(a.to(DEV), w.to(DEV), out_dtype=torch.float32), g["c_fwd"]),
+                     (FU.fused_int8_gemm(a.to(DEV), b3.to(DEV), out_dtype=torch.float32), g["c_bwd"])):
+        assert R.rel_fro(got.cpu(), torch.as_tensor(ref)) < 1e-5
+    assert R.rel_fro(FU.fwd_32(a.to(DEV), w.to(DEV)).cpu().float(), torch.as_tensor(g["c_fwd"])) < TOL_BF16
+    assert R.rel_fro(FU.bwd_33(a.to(DEV), b3.to(DEV)).cpu().float(), torch.as_tensor(g["c_bwd"])) < TOL_BF16
 
 
 def test_reference_acceptance_gate():

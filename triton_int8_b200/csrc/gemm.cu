@@ -242,6 +242,7 @@ struct __align__(8) SharedCtl {
 constexpr int K_ROWCOL = 0;      // one drain per tile, (float(acc)*a_s[m])*b_s[n]
 constexpr int K_BLOCK_GEN = 1;   // block-scaled, any scale layout, reference operation order, dumps
 constexpr int K_BLOCK_FAST = 2;  // block-scaled, one scalar factor per (tile, K block) and 64-column group
+constexpr int K_BLOCK_COLFAC = 3;  // block-scaled, per-tile A scale x per-(column, K block) B scale (fused forward)
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
@@ -289,8 +290,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // CTA pair: rank 0 (the leader) owns the operand-ready and accumulator-free barriers and issues the MMAs
   const uint32_t rank = TWO ? cluster_ctarank() : 0u;
   const bool leader = rank == 0;
-  const int unit = TWO ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;      // tile-processing unit (CTA or pair)
-  const int n_units = TWO ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  // tile-processing unit (CTA or pair) and their count: read from the special registers at each use
+  // instead of being kept live (the epilogue runs at its register budget)
+#define I8L_UNIT (TWO ? (int)(blockIdx.x >> 1) : (int)blockIdx.x)
+#define I8L_N_UNITS (TWO ? (int)(gridDim.x >> 1) : (int)gridDim.x)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -327,9 +330,13 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // tiles of this unit: m_blocks counts 128-row blocks; a pair takes two consecutive ones
   const int total_tiles = (TWO ? p.m_blocks / 2 : p.m_blocks) * p.n_tiles;
   auto unit_tile = [&](int t) {  // 128-row block of THIS CTA and 256-column tile
-    TileCoord tc = tile_coord(t, TWO ? p.m_blocks / 2 : p.m_blocks, p);
-    if (TWO) tc.m_blk = 2 * tc.m_blk + (int)rank;
-    return tc;
+    if constexpr (TWO) {
+      TileCoord tc = tile_coord(t, p.m_blocks / 2, p);
+      tc.m_blk = 2 * tc.m_blk + (int)cluster_ctarank();
+      return tc;
+    } else {
+      return tile_coord(t, p.m_blocks, p);
+    }
   };
   const int KB = p.KB;
 
@@ -341,7 +348,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       uint32_t ph = 0;
       uint32_t issued = 0, issued_ph = 0;  // bit s: a load into stage s is (or was) in flight, with parity
       bool ok = true;
-      for (int t = unit; t < total_tiles && ok; t += n_units) {
+      for (int t = I8L_UNIT; t < total_tiles && ok; t += I8L_N_UNITS) {
         const TileCoord tc = unit_tile(t);
         const int a_row = tc.m_blk * BM;
         const int b_row = (p.b_batched ? (tc.m_blk / p.mpb) * p.N : 0) + tc.n_tile * BN + (TWO ? (int)rank * BM : 0);
@@ -378,7 +385,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int s = 0, ab = 0;
       uint32_t ph = 0, aph = 0;
       bool ok = true;
-      for (int t = unit; t < total_tiles && ok; t += n_units) {
+      for (int t = I8L_UNIT; t < total_tiles && ok; t += I8L_N_UNITS) {
         for (int kb = 0; kb < KB; ++kb) {
           const bool drain_start = BLOCK || kb == 0, drain_end = BLOCK || kb == KB - 1;
           if (drain_start) {
@@ -436,7 +443,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         else mbar_arrive(smem_u32(&ctl.tempty[ab]));
       }
     };
-    for (int t = unit; t < total_tiles && ok; t += n_units) {
+    for (int t = I8L_UNIT; t < total_tiles && ok; t += I8L_N_UNITS) {
       const TileCoord tc = unit_tile(t);
       const int batch = tc.m_blk / p.mpb;
       const int64_t row = (int64_t)tc.m_blk * BM + tix;  // row in the folded [batch*M] space
@@ -451,6 +458,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
 
       if constexpr (KIND == K_BLOCK_FAST) {
+        // one scalar factor a_s * b_s per (tile, K block) and column group
         const float* as_ptr = p.a_scale + (p.a_kind == I8L_ASCALE_TILE ? (int64_t)tc.m_blk : row) * KB;
         const float* bs_ptr = p.b_scale + (bcol0 >> 7) * KB;
         float2 acc[EPI_COLS / 2];
@@ -494,6 +502,69 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             out[2 * j + 1] = acc[j].y;
           }
           store_cols(p, out, chan ? ctl.bscale[wg] : nullptr, row, col0);
+        }
+      } else if constexpr (KIND == K_BLOCK_COLFAC) {
+        constexpr bool COLFAC = true;
+        // factor of a K block: a_s * b_s, or its reciprocal when the scales are multipliers (fused
+        // variants: acc += P / (s_a * s_b); the reciprocal replaces the reference's division, 1 ulp)
+        const float* as_ptr = p.a_scale + (p.a_kind == I8L_ASCALE_TILE ? (int64_t)tc.m_blk : row) * KB;
+        const int64_t bcol = bcol0 + (tix & (EPI_COLS - 1));  // COLFAC: the column whose factor this thread publishes
+        const float* bs_ptr = COLFAC ? p.b_scale + (p.b_kind == I8L_BSCALE_GROUP ? bcol : bcol >> 7) * KB
+                                     : p.b_scale + (bcol0 >> 7) * KB;
+        const bool use_b = COLFAC ? active : (!chan && active);
+        const bool recip = COLFAC && p.divide;
+        auto factor = [&](int d) {
+          float f = __ldg(as_ptr + d);
+          if (use_b) f *= __ldg(bs_ptr + d);
+          if (COLFAC) f = recip ? __frcp_rn(f) : f;
+          return f;
+        };
+        float2 acc[EPI_COLS / 2];
+#pragma unroll
+        for (int j = 0; j < EPI_COLS / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+        float f_next = factor(0);
+        for (int d = 0; d < KB; ++d) {
+          const float f = f_next;
+          if (d + 1 < KB) f_next = factor(d + 1);
+          if (COLFAC) {  // thread i < 64 publishes the factor of column i of this group for this K block
+            if (tix < EPI_COLS) ctl.bstep[wg][d & 1][tix] = f;
+            named_sync(1 + wg, 128);
+          }
+          if (!(ok = mbar_wait(smem_u32(&ctl.tfull[ab]), aph, abort_flag))) break;
+          tc_fence_after();
+          if (active) {
+            const uint32_t taddr = tmem_base + lane_addr + ab * BN + wg * EPI_COLS;
+            const float2 f2 = make_float2(f, f);
+            const float2* fcol = reinterpret_cast<const float2*>(ctl.bstep[wg][d & 1]);
+#pragma unroll
+            for (int c = 0; c < EPI_COLS / 16; ++c) {
+              uint32_t r[16];
+              tc_ld16(taddr + c * 16, r);
+              tc_ld_wait();
+              if (c == EPI_COLS / 16 - 1) release_accumulator();
+              // one conversion and half a packed FMA per accumulator element; each pass is a run of
+              // independent instructions
+              float v[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = __int2float_rn((int)r[j]);
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                acc[c * 8 + j] = __ffma2_rn(make_float2(v[2 * j], v[2 * j + 1]), COLFAC ? fcol[c * 8 + j] : f2, acc[c * 8 + j]);
+            }
+          } else {
+            release_accumulator();
+          }
+          ab ^= 1;
+          if (ab == 0) aph ^= 1u;
+        }
+        if (ok && active) {
+          float out[EPI_COLS];
+#pragma unroll
+          for (int j = 0; j < EPI_COLS / 2; ++j) {
+            out[2 * j] = acc[j].x;
+            out[2 * j + 1] = acc[j].y;
+          }
+          store_cols(p, out, (!COLFAC && chan) ? ctl.bscale[wg] : nullptr, row, col0);
         }
       } else {
         // ---- generic paths: reference operation order, per-column / per-step scales, dumps, row x column
@@ -589,6 +660,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   }
 
+#undef I8L_UNIT
+#undef I8L_N_UNITS
   tc_fence_before();
   __syncthreads();
   if (TWO) cluster_sync_all();  // no remote arrival or tensor-memory write of the pair is still pending
@@ -720,12 +793,13 @@ static int launch_gemm(bool block, const int8_t* a_q, const int8_t* b_q, GemmPar
     p.raster = two ? blocks / 2 : blocks;
   }
   const int64_t tiles = (int64_t)(two ? p.m_blocks / 2 : p.m_blocks) * p.n_tiles;
-  const bool scalar_factor = block && !p.exact && !p.divide && !p.dump && p.b_kind != I8L_BSCALE_GROUP;
-#define I8L_LAUNCH(KIND) (two ? launch_kind<KIND, true>(ma, mb, p, tiles, st) : launch_kind<KIND, false>(ma, mb, p, tiles, st))
-  if (!block) return I8L_LAUNCH(K_ROWCOL);
-  if (scalar_factor) return I8L_LAUNCH(K_BLOCK_FAST);
-  return I8L_LAUNCH(K_BLOCK_GEN);
-#undef I8L_LAUNCH
+  const bool scalar_factor = block && !p.exact && !p.dump && !p.divide && p.b_kind != I8L_BSCALE_GROUP;
+  const bool column_factor = block && !p.exact && !p.dump && !scalar_factor && p.a_kind == I8L_ASCALE_TILE &&
+                             p.b_kind != I8L_BSCALE_CHANNEL;
+  if (!block) return two ? launch_kind<K_ROWCOL, true>(ma, mb, p, tiles, st) : launch_kind<K_ROWCOL, false>(ma, mb, p, tiles, st);
+  if (scalar_factor) return launch_kind<K_BLOCK_FAST, false>(ma, mb, p, tiles, st);
+  if (column_factor) return launch_kind<K_BLOCK_COLFAC, false>(ma, mb, p, tiles, st);
+  return launch_kind<K_BLOCK_GEN, false>(ma, mb, p, tiles, st);
 }
 
 }  // namespace i8l
@@ -744,7 +818,7 @@ extern "C" int i8l_gemm_block(const int8_t* a_q, const int8_t* b_q, const float*
   GemmParams p{};
   p.a_scale = a_scale; p.b_scale = b_scale; p.bias = static_cast<const __nv_bfloat16*>(bias); p.c = c;
   p.status = status; p.a_kind = a_scale_kind; p.b_kind = b_scale_kind; p.b_batched = b_batched ? 1 : 0;
-  p.exact = (flags & (I8L_GEMM_EXACT_ORDER | I8L_GEMM_DIVIDE)) ? 1 : 0;
+  p.exact = (flags & I8L_GEMM_EXACT_ORDER) ? 1 : 0;
   p.divide = (flags & I8L_GEMM_DIVIDE) ? 1 : 0;
   p.out_f32 = (flags & I8L_GEMM_OUT_F32) ? 1 : 0;
   p.post_scale = post_scale;

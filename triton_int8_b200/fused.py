@@ -15,11 +15,13 @@ from . import kernels as K
 from .block_channel import calc_diff  # noqa: F401
 
 
-def fused_int8_gemm(A_bf: torch.Tensor, B_bf: torch.Tensor, out_dtype=torch.bfloat16):
+def fused_int8_gemm(A_bf: torch.Tensor, B_bf: torch.Tensor, out_dtype=torch.bfloat16, exact: bool = False):
     """A_bf [B, M, K]; B_bf [N, K] (fwd: per (row, 128-K) scales, triton/fused_triton_fwd32.py:57-59)
-    or [B, N, K] (bwd: per 128x128 tile, triton/fused_triton_bwd33.py:54-56)."""
+    or [B, N, K] (bwd: per 128x128 tile, triton/fused_triton_bwd33.py:54-56).  exact=True divides per
+    element in the reference's operation order (bit-equal fp32); the default multiplies by the rounded
+    reciprocal of s_a*s_b and fuses the accumulation (same integers, ~1e-7 relative difference)."""
     aq, a_s, _, _ = K.quant_tile(A_bf, L.GRAN_TILE128, L.QMODE_FUSED)
-    flags = L.GEMM_DIVIDE | (L.GEMM_OUT_F32 if out_dtype == torch.float32 else 0)
+    flags = L.GEMM_DIVIDE | (L.GEMM_EXACT_ORDER if exact else 0) | (L.GEMM_OUT_F32 if out_dtype == torch.float32 else 0)
     if B_bf.dim() == 2:
         bq, b_s, _, _ = K.quant_tile(B_bf[None], L.GRAN_GROUP128, L.QMODE_FUSED)
         return K.gemm_block(aq, bq[0], a_s, b_s[0], L.ASCALE_TILE, L.BSCALE_GROUP, flags=flags)
