@@ -43,9 +43,9 @@ constexpr int MAX_STAGES = 6;
 constexpr int EPI_WARPS = 16;                 // four groups of four warps, 64 accumulator columns per group
 constexpr int EPI_COLS = BN / (EPI_WARPS / 4);
 constexpr int THREADS = 128 + 32 * EPI_WARPS;
+constexpr int FAC_MAX = 512;                  // K blocks whose factors are staged in shared memory at a time
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_DYN = 4 * (A_STAGE + BN * BK) + 1024;  // == 6 * (16 KB + 16 KB) + 1024
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
 struct GemmParams {
   const float* a_scale;
@@ -60,6 +60,7 @@ struct GemmParams {
   int a_kind, b_kind, b_batched;
   int exact, divide, out_f32, dump;  // dump: 0 none, 1 whole-K int32, 2 per-K-block int32
   int raster;
+  int c_align32;  // the output pointer is 32-byte aligned: 256-bit stores
   float post_scale;
 };
 
@@ -75,41 +76,47 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// One poll.  The hint lets the hardware keep the thread suspended (off the issue slots) for up to
-// ~1 ms while the phase is incomplete; it resumes as soon as the phase completes.
+// One poll: returns when the phase has completed or after the hardware's own time limit.  HINT adds
+// a suspend-time hint operand: it measured 1.3 % faster for the whole-K kernels (long waits by idle
+// warps) and 1 % slower for the block-scaled ones (short waits on the critical path).
+template <bool HINT>
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(1000000u)
-      : "memory");
+  if (HINT) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(1000000u)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+  }
   return ok;
 }
-__device__ __forceinline__ unsigned long long globaltimer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait.  Returns false when the abort flag is (or becomes) set.  The wall-clock timer is
-// slow to read, so it stays off the fast path: it is first consulted after 256 failed polls.
+// Bounded wait.  A poll whose phase is incomplete parks the thread in hardware (about 4 us on a
+// B200, whatever suspend-time hint is given) and returns early when the phase completes, so a wait
+// is one instruction in the common case and the loop below runs only for waits longer than that.
+// The limit is a poll count (2^19 polls, about 2 s): no timer, no 64-bit arithmetic in the hot loops.
+// Returns false when the limit is hit or another warp has set the abort flag.
+constexpr uint32_t WAIT_MAX_POLLS = 1u << 19;
+template <bool HINT = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
-  unsigned long long t0 = 0;
-  for (uint32_t spin = 1;; ++spin) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 255u) == 0) {
-      if (*abort_flag) return false;
-      const unsigned long long now = globaltimer();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > limit_ns) {
-        *abort_flag = 1;
-        return false;
-      }
-    }
+                                          uint32_t max_polls = WAIT_MAX_POLLS) {
+  if (mbar_try_wait<HINT>(bar, parity)) return true;
+  for (uint32_t spin = 1; spin < max_polls; ++spin) {
+    if (mbar_try_wait<HINT>(bar, parity)) return true;
+    if ((spin & 63u) == 0 && *abort_flag) return false;
   }
+  *abort_flag = 1;
+  return false;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile(
@@ -173,18 +180,6 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t adesc, uint6
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -193,6 +188,12 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
+}
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
 }
 __device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void named_sync(int id, int nthreads) {
@@ -236,12 +237,14 @@ struct __align__(8) SharedCtl {
   int abort_flag;
   float bscale[EPI_WARPS / 4][EPI_COLS];     // per-tile column scales of each epilogue group (CHANNEL)
   float bstep[EPI_WARPS / 4][2][EPI_COLS];   // per-K-block column scales (GROUP), double buffered
+  float fac[EPI_WARPS / 4][FAC_MAX];         // per-K-block scalar factors of the current tile (K_BLOCK_FAST)
 };
 
 // Epilogue kinds.  Everything but K_ROWCOL drains the accumulator every 128-wide K block.
 constexpr int K_ROWCOL = 0;      // one drain per tile, (float(acc)*a_s[m])*b_s[n]
 constexpr int K_BLOCK_GEN = 1;   // block-scaled, any scale layout, reference operation order, dumps
 constexpr int K_BLOCK_FAST = 2;  // block-scaled, one scalar factor per (tile, K block) and 64-column group
+constexpr int K_BLOCK_ROWFAC = 4;  // block-scaled, per-(row, K block) A scale x per-tile or per-channel B scale
 constexpr int K_BLOCK_COLFAC = 3;  // block-scaled, per-tile A scale x per-(column, K block) B scale (fused forward)
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
@@ -249,14 +252,22 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// Final rescale, bias, cast and store of one thread's EPI_COLS consecutive columns.
+__device__ __forceinline__ void st_global_256(void* ptr, const uint32_t* w) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
+
+// Final rescale, bias, cast and store of one thread's EPI_COLS consecutive columns.  Every lane of
+// a warp writes a different row, so each store instruction touches 32 lines: 32-byte stores (whole
+// sectors, half as many instructions) are used when the output pointer allows them.
 __device__ __forceinline__ void store_cols(const GemmParams& p, const float* acc, const float* bscale_or_null,
                                            int64_t row, int col0) {
 #pragma unroll
-  for (int j0 = 0; j0 < EPI_COLS; j0 += 8) {
-    float v[8];
+  for (int j0 = 0; j0 < EPI_COLS; j0 += 16) {
+    float v[16];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < 16; ++j) {
       v[j] = acc[j0 + j];
       if (bscale_or_null) v[j] *= bscale_or_null[j0 + j];
       if (p.post_scale != 1.f) v[j] = __fmul_rn(v[j], p.post_scale);
@@ -264,12 +275,24 @@ __device__ __forceinline__ void store_cols(const GemmParams& p, const float* acc
     }
     if (p.out_f32) {
       float* o = static_cast<float*>(p.c) + row * p.N + col0 + j0;
-      *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
-      *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      if (p.c_align32) {
+        st_global_256(o, reinterpret_cast<const uint32_t*>(v));
+        st_global_256(o + 8, reinterpret_cast<const uint32_t*>(v + 8));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      }
     } else {
       __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.c) + row * p.N + col0 + j0;
-      *reinterpret_cast<uint4*>(o) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
-                                                pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+      uint32_t w[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+      if (p.c_align32) {
+        st_global_256(o, w);
+      } else {
+        *reinterpret_cast<uint4*>(o) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(o + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+      }
     }
   }
 }
@@ -353,7 +376,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int a_row = tc.m_blk * BM;
         const int b_row = (p.b_batched ? (tc.m_blk / p.mpb) * p.N : 0) + tc.n_tile * BN + (TWO ? (int)rank * BM : 0);
         for (int kb = 0; kb < KB; ++kb) {
-          if (!(ok = mbar_wait(smem_u32(&ctl.empty[s]), ph ^ 1u, abort_flag))) break;
+          if (!(ok = mbar_wait<!BLOCK>(smem_u32(&ctl.empty[s]), ph ^ 1u, abort_flag))) break;
           if (lane == 0) {
             const uint32_t bar = smem_u32(&ctl.full[s]);
             if (TWO) {  // both CTAs' copies complete on the leader's barrier, which expects the bytes of both
@@ -377,7 +400,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int k = 0; k < STAGES; ++k)
           if (issued & (1u << k)) {
             int dummy = 0;
-            mbar_wait(smem_u32(&ctl.full[k]), (issued_ph >> k) & 1u, &dummy, 100000000ull);
+            mbar_wait(smem_u32(&ctl.full[k]), (issued_ph >> k) & 1u, &dummy, 1u << 15);
           }
       }
     } else if (warp == 1 && leader) {
@@ -388,10 +411,15 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       for (int t = I8L_UNIT; t < total_tiles && ok; t += I8L_N_UNITS) {
         for (int kb = 0; kb < KB; ++kb) {
           const bool drain_start = BLOCK || kb == 0, drain_end = BLOCK || kb == KB - 1;
-          if (drain_start) {
-            if (!(ok = mbar_wait(smem_u32(&ctl.tempty[ab]), aph ^ 1u, abort_flag))) break;
+          // block-scaled kinds wait for the accumulator buffer last (the epilogue's release is what holds
+          // the next MMA up); the whole-K kinds measured 0.7 % faster the other way round
+          if (!BLOCK && drain_start) {
+            if (!(ok = mbar_wait<!BLOCK>(smem_u32(&ctl.tempty[ab]), aph ^ 1u, abort_flag))) break;
           }
-          if (!(ok = mbar_wait(smem_u32(&ctl.full[s]), ph, abort_flag))) break;
+          if (!(ok = mbar_wait<!BLOCK>(smem_u32(&ctl.full[s]), ph, abort_flag))) break;
+          if (BLOCK) {
+            if (!(ok = mbar_wait<!BLOCK>(smem_u32(&ctl.tempty[ab]), aph ^ 1u, abort_flag))) break;
+          }
           tc_fence_after();
           if (lane == 0) {
             const uint64_t da = smem_desc(smem_a + s * A_STAGE), db = smem_desc(smem_b + s * B_STAGE);
@@ -443,6 +471,90 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         else mbar_arrive(smem_u32(&ctl.tempty[ab]));
       }
     };
+    if constexpr (KIND == K_BLOCK_FAST) {
+      // One scalar factor per (tile, K block) and column group: a per-tile A scale times a per-tile or
+      // per-channel B scale.  The K-block loop keeps only the accumulators, one chunk of tensor-memory
+      // data and a few scalars live: the factors of the tile are staged in shared memory first, and
+      // what the final store needs is recomputed from the tile index afterwards.
+      const uint32_t tfull0 = smem_u32(&ctl.tfull[0]), tempty0 = smem_u32(&ctl.tempty[0]);
+      // Values derived from the thread index pass through an empty asm statement: the compiler then
+      // keeps them in registers instead of recomputing them from the special register at every use
+      // inside the K-block loop (which cost about 35 ALU instructions per warp and K block).
+      uint32_t taddr0 = tmem_base + lane_addr + wg * EPI_COLS, fac0 = smem_u32(&ctl.fac[wg][0]), lane0 = lane == 0;
+      asm volatile("" : "+r"(taddr0), "+r"(fac0), "+r"(lane0));
+      const bool chan = p.b_kind == I8L_BSCALE_CHANNEL;
+      constexpr int CH = 8;
+      for (int t = I8L_UNIT; t < total_tiles && ok; t += I8L_N_UNITS) {
+        float2 acc[EPI_COLS / 2];
+#pragma unroll
+        for (int j = 0; j < EPI_COLS / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+        bool active = true;
+        for (int k0 = 0; k0 < KB && ok; k0 += FAC_MAX) {
+          const int dn = KB - k0 < FAC_MAX ? KB - k0 : FAC_MAX;
+          {
+            const TileCoord tc = unit_tile(t);
+            const int col0 = tc.n_tile * BN + wg * EPI_COLS;
+            active = col0 < p.N;
+            const int64_t bcol0 = (int64_t)(p.b_batched ? tc.m_blk / p.mpb : 0) * p.N + col0;
+            named_sync(1 + wg, 128);  // the group is done with the previous contents
+            if (k0 == 0 && chan && tix < EPI_COLS) ctl.bscale[wg][tix] = active ? __ldg(p.b_scale + bcol0 + tix) : 0.f;
+            const float* as_ptr = p.a_scale + (int64_t)tc.m_blk * KB + k0;
+            const float* bs_ptr = p.b_scale + (bcol0 >> 7) * KB + k0;
+            for (int i = tix; i < dn; i += 128)
+              ctl.fac[wg][i] = __ldg(as_ptr + i) * ((!chan && active) ? __ldg(bs_ptr + i) : 1.f);
+            named_sync(1 + wg, 128);
+          }
+          for (int d = 0; d < dn; ++d) {
+            float f;
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(f) : "r"(fac0 + 4 * d));
+            // no early exit: a loop with one exit keeps the 64 accumulators where they are; after a
+            // timeout the remaining K blocks are skipped without further waits
+            ok = ok && mbar_wait(tfull0 + 8 * ab, aph, abort_flag);
+            tc_fence_after();
+            auto release = [&]() {  // all of this warp's tensor-memory loads of the buffer have completed
+              tc_fence_before();
+              __syncwarp();
+              if (lane0) mbar_arrive(tempty0 + 8 * ab);
+            };
+            if (ok && active) {
+              const uint32_t taddr = taddr0 + ab * BN;
+              const float2 f2 = make_float2(f, f);
+#pragma unroll
+              for (int c = 0; c < EPI_COLS / CH; ++c) {  // 8-column chunks: 16-column ones spill here
+                uint32_t r[CH];
+                tc_ld8(taddr + c * CH, r);
+                tc_ld_wait();
+                if (c == EPI_COLS / CH - 1) release();
+                // one conversion and half a packed FMA per accumulator element; each pass is a run of
+                // independent instructions
+                float v[CH];
+#pragma unroll
+                for (int j = 0; j < CH; ++j) v[j] = __int2float_rn((int)r[j]);
+#pragma unroll
+                for (int j = 0; j < CH / 2; ++j)
+                  acc[c * (CH / 2) + j] = __ffma2_rn(make_float2(v[2 * j], v[2 * j + 1]), f2, acc[c * (CH / 2) + j]);
+              }
+            } else {
+              release();
+            }
+            ab ^= 1;
+            if (ab == 0) aph ^= 1u;
+          }
+        }
+        if (ok && active) {
+          int t2 = t;
+          asm volatile("" : "+r"(t2));  // keeps the tile's coordinates out of the K-block loop's live registers
+          const TileCoord tc = unit_tile(t2);
+          float out[EPI_COLS];
+#pragma unroll
+          for (int j = 0; j < EPI_COLS / 2; ++j) {
+            out[2 * j] = acc[j].x;
+            out[2 * j + 1] = acc[j].y;
+          }
+          store_cols(p, out, chan ? ctl.bscale[wg] : nullptr, (int64_t)tc.m_blk * BM + tix, tc.n_tile * BN + wg * EPI_COLS);
+        }
+      }
+    } else
     for (int t = I8L_UNIT; t < total_tiles && ok; t += I8L_N_UNITS) {
       const TileCoord tc = unit_tile(t);
       const int batch = tc.m_blk / p.mpb;
@@ -457,8 +569,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         named_sync(1 + wg, 128);
       }
 
-      if constexpr (KIND == K_BLOCK_FAST) {
-        // one scalar factor a_s * b_s per (tile, K block) and column group
+      if constexpr (KIND == K_BLOCK_ROWFAC) {
+        // one factor a_s * b_s per (row or tile, K block) and column group, fetched by each thread
         const float* as_ptr = p.a_scale + (p.a_kind == I8L_ASCALE_TILE ? (int64_t)tc.m_blk : row) * KB;
         const float* bs_ptr = p.b_scale + (bcol0 >> 7) * KB;
         float2 acc[EPI_COLS / 2];
@@ -468,9 +580,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int d = 0; d < KB; ++d) {
           const float f = f_next;
           if (d + 1 < KB) f_next = __ldg(as_ptr + d + 1) * ((!chan && active) ? __ldg(bs_ptr + d + 1) : 1.f);
-          if (!(ok = mbar_wait(smem_u32(&ctl.tfull[ab]), aph, abort_flag))) break;
+          ok = ok && mbar_wait<!BLOCK>(smem_u32(&ctl.tfull[ab]), aph, abort_flag);  // single-exit loop, see K_BLOCK_FAST
           tc_fence_after();
-          if (active) {
+          if (ok && active) {
             const uint32_t taddr = tmem_base + lane_addr + ab * BN + wg * EPI_COLS;
             const float2 f2 = make_float2(f, f);
 #pragma unroll
@@ -530,9 +642,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (tix < EPI_COLS) ctl.bstep[wg][d & 1][tix] = f;
             named_sync(1 + wg, 128);
           }
-          if (!(ok = mbar_wait(smem_u32(&ctl.tfull[ab]), aph, abort_flag))) break;
+          ok = ok && mbar_wait<!BLOCK>(smem_u32(&ctl.tfull[ab]), aph, abort_flag);  // single-exit loop, see K_BLOCK_FAST
           tc_fence_after();
-          if (active) {
+          if (ok && active) {
             const uint32_t taddr = tmem_base + lane_addr + ab * BN + wg * EPI_COLS;
             const float2 f2 = make_float2(f, f);
             const float2* fcol = reinterpret_cast<const float2*>(ctl.bstep[wg][d & 1]);
@@ -585,7 +697,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               named_sync(1 + wg, 128);
             }
           }
-          if (!(ok = mbar_wait(smem_u32(&ctl.tfull[ab]), aph, abort_flag))) break;
+          if (!(ok = mbar_wait<!BLOCK>(smem_u32(&ctl.tfull[ab]), aph, abort_flag))) break;
           tc_fence_after();
           const uint32_t taddr = tmem_base + lane_addr + ab * BN + wg * EPI_COLS;
 #pragma unroll
@@ -785,6 +897,7 @@ static int launch_gemm(bool block, const int8_t* a_q, const int8_t* b_q, GemmPar
   p.M = (int)M;
   p.N = (int)N;
   p.KB = (int)(K / 128);
+  p.c_align32 = (reinterpret_cast<uintptr_t>(p.c) & 31u) == 0;
   // M-units (128-row blocks, or 256-row pair blocks) per raster group: the group's A panel should stay
   // L2-resident while the N tiles are swept (measured best: 4096 rows at K = 8192, flat for deeper K).
   {
@@ -797,7 +910,8 @@ static int launch_gemm(bool block, const int8_t* a_q, const int8_t* b_q, GemmPar
   const bool column_factor = block && !p.exact && !p.dump && !scalar_factor && p.a_kind == I8L_ASCALE_TILE &&
                              p.b_kind != I8L_BSCALE_CHANNEL;
   if (!block) return two ? launch_kind<K_ROWCOL, true>(ma, mb, p, tiles, st) : launch_kind<K_ROWCOL, false>(ma, mb, p, tiles, st);
-  if (scalar_factor) return launch_kind<K_BLOCK_FAST, false>(ma, mb, p, tiles, st);
+  if (scalar_factor && p.a_kind == I8L_ASCALE_TILE) return launch_kind<K_BLOCK_FAST, false>(ma, mb, p, tiles, st);
+  if (scalar_factor) return launch_kind<K_BLOCK_ROWFAC, false>(ma, mb, p, tiles, st);
   if (column_factor) return launch_kind<K_BLOCK_COLFAC, false>(ma, mb, p, tiles, st);
   return launch_kind<K_BLOCK_GEN, false>(ma, mb, p, tiles, st);
 }
