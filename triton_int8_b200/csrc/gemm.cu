@@ -484,12 +484,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       asm volatile("" : "+r"(taddr0), "+r"(fac0), "+r"(lane0));
       const bool chan = p.b_kind == I8L_BSCALE_CHANNEL;
       constexpr int CH = 8;
-      for (int t = I8L_UNIT; t < total_tiles && ok; t += I8L_N_UNITS) {
+      // The loops below never exit early: the warps of a column group meet at named barriers, so after a
+      // wait timeout (`ok` false) a warp runs through the remaining tiles without waiting or computing.
+      for (int t = I8L_UNIT; t < total_tiles; t += I8L_N_UNITS) {
         float2 acc[EPI_COLS / 2];
 #pragma unroll
         for (int j = 0; j < EPI_COLS / 2; ++j) acc[j] = make_float2(0.f, 0.f);
         bool active = true;
-        for (int k0 = 0; k0 < KB && ok; k0 += FAC_MAX) {
+        for (int k0 = 0; k0 < KB; k0 += FAC_MAX) {
           const int dn = KB - k0 < FAC_MAX ? KB - k0 : FAC_MAX;
           {
             const TileCoord tc = unit_tile(t);
@@ -555,7 +557,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
     } else
-    for (int t = I8L_UNIT; t < total_tiles && ok; t += I8L_N_UNITS) {
+    for (int t = I8L_UNIT; t < total_tiles; t += I8L_N_UNITS) {  // no early exit either (named barriers inside)
       const TileCoord tc = unit_tile(t);
       const int batch = tc.m_blk / p.mpb;
       const int64_t row = (int64_t)tc.m_blk * BM + tix;  // row in the folded [batch*M] space
@@ -697,18 +699,19 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               named_sync(1 + wg, 128);
             }
           }
-          if (!(ok = mbar_wait<!BLOCK>(smem_u32(&ctl.tfull[ab]), aph, abort_flag))) break;
+          ok = ok && mbar_wait<!BLOCK>(smem_u32(&ctl.tfull[ab]), aph, abort_flag);
           tc_fence_after();
+          const bool live = ok && active;
           const uint32_t taddr = tmem_base + lane_addr + ab * BN + wg * EPI_COLS;
 #pragma unroll
           for (int c = 0; c < EPI_COLS / 16; ++c) {
             uint32_t r[16];
-            if (active) {
+            if (live) {
               tc_ld16(taddr + c * 16, r);
               tc_ld_wait();
             }
             if (c == EPI_COLS / 16 - 1) release_accumulator();
-            if (!active) continue;
+            if (!live) continue;
             if (BLOCK) {
               if (p.dump) {
                 int32_t* o = static_cast<int32_t*>(p.c) +
