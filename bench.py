@@ -193,6 +193,9 @@ def main():
     ap.add_argument("--hadamard", type=int, default=None, choices=[0, 128],
                     help="128-point rotation in front of every quantizer (default: 128 for c3 and c5, as BASELINE.json "
                          "describes those configurations; 0 otherwise)")
+    ap.add_argument("--reduce-scatter", default="nccl", choices=["peer", "nccl"],
+                    help="N>1: dX partials scattered by the GEMM epilogue into peer memory (default; falls back to\n"
+                         "nccl when the peer mapping cannot be set up), or a separate NCCL reduce-scatter")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -226,6 +229,20 @@ def main():
     Nl = hi - lo
     x, w, dy = make_inputs(M, K, Nl, rank, dev)
     step_obj = tp.ColumnParallelStep(None if world == 1 else dist.group.WORLD, DEFAULT)
+    peer_slots, rs_mode = None, "none"
+    if world > 1:
+        rs_mode = "nccl reduce_scatter_tensor on a side stream, overlapped with the dW GEMM"
+        if args.reduce_scatter == "peer" and not args.workload.startswith("c2"):
+            try:
+                peer_slots = tp.PeerSlots(M, K)
+                rs_mode = f"dX GEMM epilogue stores into peer slots ({peer_slots.mapping}) + local slot sum"
+            except Exception as exc:  # noqa: BLE001 - report and use the NCCL route
+                print(f"[bench] peer slots unavailable on rank {rank}: {exc!r}; using NCCL", file=sys.stderr)
+        if world > 1:   # all ranks must take the same route
+            flag = torch.tensor([1.0 if peer_slots is not None else 0.0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if flag.item() == 0.0 and peer_slots is not None:
+                peer_slots, rs_mode = None, "nccl reduce_scatter_tensor on a side stream, overlapped with the dW GEMM"
 
     def sync_all():
         torch.cuda.synchronize()
@@ -289,9 +306,15 @@ def main():
         dy_op, dyt_op = quantize_grad_output(dy, cfg, True, True)
         wtq, wts = Kn.quant_col_t(w, cfg.qmode, had)
         if record: e[2].record()
-        dx_partial = Kn.gemm_block(dy_op[0], wtq, dy_op[1], wts, L.ASCALE_TILE, L.BSCALE_CHANNEL, None, cfg.post)[0]
-        if record: e[3].record()
-        if world > 1:
+        if peer_slots is not None:
+            dx = peer_slots.reduce_scatter_gemm(dy_op[0], dy_op[1], wtq, wts, L.ASCALE_TILE, cfg.post)
+            if record: e[3].record()
+        else:
+            dx_partial = Kn.gemm_block(dy_op[0], wtq, dy_op[1], wts, L.ASCALE_TILE, L.BSCALE_CHANNEL, None, cfg.post)[0]
+            if record: e[3].record()
+        if peer_slots is not None:
+            pass
+        elif world > 1:
             main = torch.cuda.current_stream()
             step_obj.comm_stream.wait_stream(main)
             with torch.cuda.stream(step_obj.comm_stream):
@@ -302,7 +325,7 @@ def main():
         if record: e[4].record()
         dw = grad_weight(dyt_op, (xqt, xst), cfg)
         if record: e[5].record()
-        if world > 1:
+        if world > 1 and peer_slots is None:
             torch.cuda.current_stream().wait_stream(step_obj.comm_stream)
         if record:
             gemm_events.append(e)
@@ -456,7 +479,7 @@ def main():
             "metric": "linear_fwd_bwd_tokens_per_s", "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": desc, "hadamard": had, "M": M, "K": K, "N": N, "N_per_gpu": Nl, "parallelism": f"tp{world}-column",
+            "config": {"workload": desc, "hadamard": had, "M": M, "K": K, "N": N, "N_per_gpu": Nl, "parallelism": f"tp{world}-column", "reduce_scatter": rs_mode,
                        "l2": "inputs (X 0.5 GB + dY >= 0.2 GB per step) exceed the 126 MB L2; no explicit flush"},
             "tops_per_gpu": tops, "gemm_ms": {"fwd": t_fwd, "dx": t_dx, "dw": t_dw},
             "roofline": roofline, "quantizers": quant, "cpu_baseline": cpu_baseline, "e2e": e2e,

@@ -175,6 +175,29 @@ I8L_API int i8l_gemm_dump_i32(const int8_t* a_q, const int8_t* b_q, int b_batche
                       int64_t batch, int64_t M, int64_t N, int64_t K, int per_block,
                       int32_t* status, void* stream);
 
+/*
+ * Column-parallel dX (one process per GPU, W split along N): the block-scaled GEMM of
+ * i8l_gemm_block (per-tile a scales, per-channel or per-tile b scales, bf16 output, batch 1) whose
+ * epilogue scatters the partial product for a reduce-scatter along M.  Row block o (rows
+ * [o*M/world, (o+1)*M/world)) is written to c_slots[o] + rank*(M/world)*N, i.e. into slot `rank` of a
+ * bf16 [world, M/world, N] buffer that lives in rank o's memory.  c_slots is a HOST array of `world`
+ * device pointers: c_slots[rank] is local, the others are peer mappings of the other ranks' buffers
+ * (CUDA IPC or symmetric memory; plain stores over NVLink, no multicast).  The caller orders the
+ * ranks around the call (all ranks' previous readers done before, all writers done after) and then
+ * sums its own buffer with i8l_sum_slots.  M must be a multiple of 128*world, world <= I8L_MAX_RANKS.
+ * No counterpart in the reference (it has no multi-GPU code).
+ */
+#define I8L_MAX_RANKS 8
+I8L_API int i8l_gemm_block_scatter(const int8_t* a_q, const int8_t* b_q, const float* a_scale, const float* b_scale,
+                           int b_scale_kind, float post_scale, void* const* c_slots, int world, int rank,
+                           int64_t M, int64_t N, int64_t K, int32_t* status, void* stream);
+
+/*
+ * out bf16 [rows, cols] = sum over w of slots bf16 [world, rows, cols], added in slot order in fp32 and
+ * rounded once (deterministic).  cols a multiple of 8.  No counterpart in the reference.
+ */
+I8L_API int i8l_sum_slots(const void* slots, void* out, int world, int64_t rows, int64_t cols, void* stream);
+
 /* Text of the calling thread's most recent error ("" if none). */
 I8L_API const char* i8l_last_error(void);
 

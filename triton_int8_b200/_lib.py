@@ -20,6 +20,7 @@ HAD_NONE, HAD_128, HAD_FULL = 0, 128, -1
 ASCALE_TILE, ASCALE_GROUP = 0, 1
 BSCALE_CHANNEL, BSCALE_TILE, BSCALE_GROUP = 0, 1, 2
 GEMM_EXACT_ORDER, GEMM_DIVIDE, GEMM_OUT_F32 = 1, 2, 4
+MAX_RANKS = 8
 
 _P, _I64, _I, _F = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float
 
@@ -32,6 +33,8 @@ SIGNATURES = {
     "i8l_gemm_block": [_P, _P, _P, _P, _I, _I, _I, _P, _F, _P, _I64, _I64, _I64, _I64, _I, _P, _P],
     "i8l_gemm_rowcol": [_P, _P, _P, _P, _I, _P, _F, _P, _I64, _I64, _I64, _I64, _I, _P, _P],
     "i8l_gemm_dump_i32": [_P, _P, _I, _P, _I64, _I64, _I64, _I64, _I, _P, _P],
+    "i8l_gemm_block_scatter": [_P, _P, _P, _P, _I, _F, _P, _I, _I, _I64, _I64, _I64, _P, _P],
+    "i8l_sum_slots": [_P, _P, _I, _I64, _I64, _P],
     "i8l_version": [],
 }
 

@@ -61,6 +61,10 @@ struct GemmParams {
   int exact, divide, out_f32, dump;  // dump: 0 none, 1 whole-K int32, 2 per-K-block int32
   int raster;
   int c_align32;  // the output pointer is 32-byte aligned: 256-bit stores
+  // scatter mode (rs_rows > 0): rows [o*rs_rows, (o+1)*rs_rows) of the product go to c_slots[o], a
+  // [world, rs_rows, N] bf16 buffer of rank o (peer memory), at slot rs_rank
+  void* c_slots[I8L_MAX_RANKS];
+  int rs_rows, rs_rank;
   float post_scale;
 };
 
@@ -262,7 +266,7 @@ __device__ __forceinline__ void st_global_256(void* ptr, const uint32_t* w) {
 // a warp writes a different row, so each store instruction touches 32 lines: 32-byte stores (whole
 // sectors, half as many instructions) are used when the output pointer allows them.
 __device__ __forceinline__ void store_cols(const GemmParams& p, const float* acc, const float* bscale_or_null,
-                                           int64_t row, int col0) {
+                                           int64_t row, int col0, void* cbase) {
 #pragma unroll
   for (int j0 = 0; j0 < EPI_COLS; j0 += 16) {
     float v[16];
@@ -274,7 +278,7 @@ __device__ __forceinline__ void store_cols(const GemmParams& p, const float* acc
       if (p.bias) v[j] = __fadd_rn(v[j], __bfloat162float(p.bias[col0 + j0 + j]));
     }
     if (p.out_f32) {
-      float* o = static_cast<float*>(p.c) + row * p.N + col0 + j0;
+      float* o = static_cast<float*>(cbase) + row * p.N + col0 + j0;
       if (p.c_align32) {
         st_global_256(o, reinterpret_cast<const uint32_t*>(v));
         st_global_256(o + 8, reinterpret_cast<const uint32_t*>(v + 8));
@@ -283,7 +287,7 @@ __device__ __forceinline__ void store_cols(const GemmParams& p, const float* acc
         for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
       }
     } else {
-      __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.c) + row * p.N + col0 + j0;
+      __nv_bfloat16* o = static_cast<__nv_bfloat16*>(cbase) + row * p.N + col0 + j0;
       uint32_t w[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) w[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
@@ -553,7 +557,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             out[2 * j] = acc[j].x;
             out[2 * j + 1] = acc[j].y;
           }
-          store_cols(p, out, chan ? ctl.bscale[wg] : nullptr, (int64_t)tc.m_blk * BM + tix, tc.n_tile * BN + wg * EPI_COLS);
+          int64_t row = (int64_t)tc.m_blk * BM + tix;
+          void* cbase = p.c;
+          if (p.rs_rows) {  // scatter mode: this 128-row block belongs to rank `owner`; write into our slot of its buffer
+            const int owner = (tc.m_blk * BM) / p.rs_rows;
+            cbase = p.c_slots[owner];
+            row += (int64_t)(p.rs_rank - owner) * p.rs_rows;
+          }
+          store_cols(p, out, chan ? ctl.bscale[wg] : nullptr, row, tc.n_tile * BN + wg * EPI_COLS, cbase);
         }
       }
     } else
@@ -615,7 +626,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             out[2 * j] = acc[j].x;
             out[2 * j + 1] = acc[j].y;
           }
-          store_cols(p, out, chan ? ctl.bscale[wg] : nullptr, row, col0);
+          store_cols(p, out, chan ? ctl.bscale[wg] : nullptr, row, col0, p.c);
         }
       } else if constexpr (KIND == K_BLOCK_COLFAC) {
         constexpr bool COLFAC = true;
@@ -678,7 +689,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             out[2 * j] = acc[j].x;
             out[2 * j + 1] = acc[j].y;
           }
-          store_cols(p, out, (!COLFAC && chan) ? ctl.bscale[wg] : nullptr, row, col0);
+          store_cols(p, out, (!COLFAC && chan) ? ctl.bscale[wg] : nullptr, row, col0, p.c);
         }
       } else {
         // ---- generic paths: reference operation order, per-column / per-step scales, dumps, row x column
@@ -769,7 +780,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (ab == 0) aph ^= 1u;
         }
         if constexpr (BLOCK) {
-          if (ok && active && !p.dump) store_cols(p, acc, nullptr, row, col0);
+          if (ok && active && !p.dump) store_cols(p, acc, nullptr, row, col0, p.c);
         }
       }
     }
@@ -785,6 +796,25 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_after();
     if (TWO) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// out[r, c] = sum over the `world` slots of slots[w, r, c], added in slot order in fp32 and rounded once:
+// the local half of the reduce-scatter whose other half is the scatter-mode GEMM epilogue.
+__global__ void __launch_bounds__(256) sum_slots_kernel(const uint4* __restrict__ slots, uint4* __restrict__ out,
+                                                        int world, int64_t n16) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int w = 0; w < world; ++w) {
+      float v[8];
+      unpack8(__ldg(slots + (int64_t)w * n16 + i), v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], v[j]);
+    }
+    out[i] = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                        pack_bf16x2(acc[6], acc[7]));
   }
 }
 
@@ -901,6 +931,8 @@ static int launch_gemm(bool block, const int8_t* a_q, const int8_t* b_q, GemmPar
   p.N = (int)N;
   p.KB = (int)(K / 128);
   p.c_align32 = (reinterpret_cast<uintptr_t>(p.c) & 31u) == 0;
+  for (int r = 0; r < I8L_MAX_RANKS; ++r)
+    if (p.rs_rows && p.c_slots[r] && (reinterpret_cast<uintptr_t>(p.c_slots[r]) & 31u)) p.c_align32 = 0;
   // M-units (128-row blocks, or 256-row pair blocks) per raster group: the group's A panel should stay
   // L2-resident while the N tiles are swept (measured best: 4096 rows at K = 8192, flat for deeper K).
   {
@@ -959,4 +991,40 @@ extern "C" int i8l_gemm_dump_i32(const int8_t* a_q, const int8_t* b_q, int b_bat
   GemmParams p{};
   p.c = out; p.status = status; p.b_batched = b_batched ? 1 : 0; p.dump = per_block ? 2 : 1; p.post_scale = 1.f;
   return launch_gemm(per_block != 0, a_q, b_q, p, batch, M, N, K, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int i8l_gemm_block_scatter(const int8_t* a_q, const int8_t* b_q, const float* a_scale, const float* b_scale,
+                                      int b_scale_kind, float post_scale, void* const* c_slots, int world, int rank,
+                                      int64_t M, int64_t N, int64_t K, int32_t* status, void* stream) {
+  if (!a_scale || !b_scale || !c_slots) return fail(I8L_ERR_ARG, "null pointer");
+  if (b_scale_kind != I8L_BSCALE_CHANNEL && b_scale_kind != I8L_BSCALE_TILE) return fail(I8L_ERR_ARG, "bad b_scale_kind");
+  if (world < 1 || world > I8L_MAX_RANKS || rank < 0 || rank >= world)
+    return fail(I8L_ERR_ARG, "rank %d of %d: at most %d ranks", rank, world, I8L_MAX_RANKS);
+  if (M <= 0 || M % ((int64_t)world * 128))
+    return fail(I8L_ERR_SHAPE, "M=%lld must split into %d row blocks that are multiples of 128", (long long)M, world);
+  GemmParams p{};
+  p.a_scale = a_scale; p.b_scale = b_scale; p.status = status;
+  p.a_kind = I8L_ASCALE_TILE; p.b_kind = b_scale_kind; p.post_scale = post_scale;
+  for (int r = 0; r < world; ++r) {
+    if (!c_slots[r] || !aligned16(c_slots[r])) return fail(I8L_ERR_ALIGN, "c_slots[%d] must be a 16-byte aligned device pointer", r);
+    p.c_slots[r] = c_slots[r];
+  }
+  p.c = c_slots[rank];
+  p.rs_rows = (int)(M / world);
+  p.rs_rank = rank;
+  return launch_gemm(true, a_q, b_q, p, 1, M, N, K, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int i8l_sum_slots(const void* slots, void* out, int world, int64_t rows, int64_t cols, void* stream) {
+  if (!slots || !out) return fail(I8L_ERR_ARG, "null pointer");
+  if (world < 1 || rows <= 0 || cols <= 0 || cols % 8) return fail(I8L_ERR_SHAPE, "world >= 1, rows > 0, cols a positive multiple of 8");
+  if (!aligned16(slots) || !aligned16(out)) return fail(I8L_ERR_ALIGN, "slots and out must be 16-byte aligned");
+  if (int e = check_arch()) return e;
+  const int64_t n16 = rows * cols / 8;
+  const int64_t want = (n16 + 255) / 256;
+  const int grid = (int)(want < 148 * 8 ? want : 148 * 8);
+  sum_slots_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(slots),
+                                                                        static_cast<uint4*>(out), world, n16);
+  I8L_CUDA_OK(cudaGetLastError());
+  return I8L_OK;
 }

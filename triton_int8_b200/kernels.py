@@ -108,3 +108,30 @@ def gemm_dump_i32(aq, bq, per_block=False, status=None):
     L.call("i8l_gemm_dump_i32", aq.data_ptr(), bq.data_ptr(), int(bb), out.data_ptr(), B, M, N, K, int(per_block),
            _ptr(status), _stream())
     return out
+
+
+def gemm_block_scatter(aq, bq, a_s, b_s, slot_ptrs, rank: int, b_kind=L.BSCALE_CHANNEL, post_scale=1.0, status=None):
+    """Block-scaled GEMM [M, K] x [N, K]^T whose row block o goes to slot `rank` of the bf16
+    [world, M/world, N] buffer at slot_ptrs[o] (device pointers, peers included).  Nothing is returned:
+    the caller synchronises the ranks and sums its own buffer with sum_slots."""
+    import ctypes
+    aq, bq = aq.contiguous(), bq.contiguous()
+    B, M, N, K, bb = _gemm_dims(aq, bq)
+    if B != 1 or bb:
+        raise ValueError("gemm_block_scatter: one batch, shared B operand")
+    world = len(slot_ptrs)
+    arr = (ctypes.c_void_p * world)(*[int(p) for p in slot_ptrs])
+    L.call("i8l_gemm_block_scatter", aq.data_ptr(), bq.data_ptr(), a_s.contiguous().data_ptr(),
+           b_s.contiguous().data_ptr(), b_kind, float(post_scale), ctypes.cast(arr, ctypes.c_void_p), world, int(rank),
+           M, N, K, _ptr(status), _stream())
+
+
+def sum_slots(slots: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """slots bf16 [world, rows, cols] -> bf16 [rows, cols], summed in slot order in fp32."""
+    if slots.dtype != torch.bfloat16 or slots.dim() != 3 or not slots.is_contiguous():
+        raise TypeError("sum_slots: contiguous bf16 [world, rows, cols]")
+    world, rows, cols = slots.shape
+    if out is None:
+        out = torch.empty((rows, cols), dtype=torch.bfloat16, device=slots.device)
+    L.call("i8l_sum_slots", slots.data_ptr(), out.data_ptr(), world, rows, cols, _stream())
+    return out

@@ -3,7 +3,9 @@
 W [N, K] is split along N: rank r owns W[r*N/g:(r+1)*N/g].  X is replicated.  The forward
 Y_r = X W_r^T and dW_r = dY_r^T X need no communication; dX = sum_r dY_r W_r is reduced with one
 reduce-scatter along M (rank r keeps rows r*M/g..(r+1)*M/g), issued on a side stream so that it
-overlaps the dW GEMM.  This is the only collective in the library (NCCL over NVLink/NVSwitch).
+overlaps the dW GEMM (NCCL over NVLink/NVSwitch), or, with `PeerSlots`, by the dX GEMM itself: its
+epilogue stores each 128-row block straight into the owning rank's memory over NVLink (plain peer
+stores into one slot per source rank) and the owner adds the slots up, so no collective kernel runs.
 The reference has no multi-GPU code; the sharding follows from its primitives
 (triton/block_channel_fwd32.py:252, triton/block_channel_bwd33.py:175).
 """
@@ -12,6 +14,8 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from . import _lib as L
+from . import kernels as K
 from .linear import DEFAULT, Int8Config, grad_input, grad_weight, linear_forward, quantize_grad_output
 
 
@@ -63,14 +67,82 @@ def set_shape_checks(on: bool) -> None:
     _DEBUG_SHAPES = bool(on)
 
 
+class PeerSlots:
+    """A bf16 [world, M/world, K] buffer on every rank, each mapped into all the others (one process per
+    GPU, one node), for the reduce-scatter that the dX GEMM's epilogue does itself.
+
+    Mapping: torch's symmetric memory when it can be set up, else CUDA IPC handles exchanged through
+    the process group.  Ordering between ranks is a one-element NCCL all-reduce on the compute stream
+    (`fence`): every rank's earlier work on that stream is complete before any rank's later work starts.
+    """
+
+    def __init__(self, rows_total: int, cols: int, group=None, device=None):
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > L.MAX_RANKS:
+            raise ValueError(f"PeerSlots: at most {L.MAX_RANKS} ranks")
+        shard_bounds(rows_total, self.world, self.rank)  # validates the split
+        self.rows, self.cols = rows_total // self.world, cols
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self._keep = []   # objects that keep the peer mappings alive
+        self.mapping = None
+        numel = self.world * self.rows * cols
+        try:
+            import torch.distributed._symmetric_memory as symm
+            buf = symm.empty((numel,), dtype=torch.bfloat16, device=self.device)
+            hdl = symm.rendezvous(buf, group if group is not None else dist.group.WORLD)
+            self.ptrs = [int(p) for p in hdl.buffer_ptrs]
+            self._keep += [hdl]
+            self.mapping = "symmetric_memory"
+        except Exception as exc:  # noqa: BLE001 - any failure of the optional route selects the other one
+            self._symm_error = repr(exc)
+            buf = torch.empty((numel,), dtype=torch.bfloat16, device=self.device)
+            self.ptrs = self._exchange_ipc(buf)
+            self.mapping = "cuda_ipc"
+        self.local = buf.view(self.world, self.rows, cols)
+        self._flag = torch.zeros(1, dtype=torch.float32, device=self.device)
+        if self.ptrs[self.rank] != buf.data_ptr():
+            raise RuntimeError("PeerSlots: the local mapping does not match the local buffer")
+
+    def _exchange_ipc(self, buf: torch.Tensor):
+        storage = buf.untyped_storage()
+        handle = storage._share_cuda_()   # (device, handle, size, offset, ...) of the allocation that holds buf
+        offset_in_alloc = handle[3]
+        infos = [None] * self.world
+        dist.all_gather_object(infos, (handle, offset_in_alloc), group=self.group)
+        ptrs = []
+        for r, (h, off) in enumerate(infos):
+            if r == self.rank:
+                ptrs.append(buf.data_ptr())
+                continue
+            peer = torch.UntypedStorage._new_shared_cuda(*h)
+            self._keep.append(peer)
+            ptrs.append(peer.data_ptr())
+        return ptrs
+
+    def fence(self) -> None:
+        """Stream-ordered barrier over the group."""
+        dist.all_reduce(self._flag, group=self.group)
+
+    def reduce_scatter_gemm(self, dyq, dys, wtq, wts, a_kind, post_scale, out=None) -> torch.Tensor:
+        """dX rows of this rank = sum over ranks of (dY_r W_r) restricted to those rows."""
+        if a_kind != L.ASCALE_TILE:
+            raise ValueError("PeerSlots needs per-tile activation scales")
+        self.fence()   # every rank has finished reading its slots of the previous step
+        K.gemm_block_scatter(dyq, wtq, dys, wts, self.ptrs, self.rank, L.BSCALE_CHANNEL, post_scale)
+        self.fence()   # every rank's stores have landed
+        return K.sum_slots(self.local, out)
+
+
 class ColumnParallelStep:
     """Forward + backward of one column-parallel linear with the dX reduce-scatter overlapped
     with the dW GEMM.  Holds the side stream and events; reuse one instance per layer."""
 
-    def __init__(self, group=None, cfg: Int8Config = DEFAULT):
+    def __init__(self, group=None, cfg: Int8Config = DEFAULT, peer_slots: PeerSlots | None = None):
         self.group, self.cfg = group, cfg
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.comm_stream = torch.cuda.Stream() if self.world > 1 else None
+        self.peer_slots = peer_slots   # when given, the dX GEMM scatters its partials itself (no NCCL reduce-scatter)
 
     def forward(self, x: torch.Tensor, w_shard: torch.Tensor, bias_shard=None):
         return linear_forward(x, w_shard, bias_shard, self.cfg, want_xt=True)
@@ -78,6 +150,10 @@ class ColumnParallelStep:
     def backward(self, dy_shard: torch.Tensor, w_shard: torch.Tensor, saved_xt):
         """Returns (dx rows owned by this rank [M/g, K], dw_shard [N/g, K])."""
         dy_op, dyt_op = quantize_grad_output(dy_shard, self.cfg, True, True)
+        if self.world > 1 and self.peer_slots is not None and not self.cfg.exact and self.cfg.a_kind == L.ASCALE_TILE:
+            wtq, wts = K.quant_col_t(w_shard, self.cfg.qmode, self.cfg.hadamard)
+            dx = self.peer_slots.reduce_scatter_gemm(dy_op[0], dy_op[1], wtq, wts, self.cfg.a_kind, self.cfg.post)
+            return dx, grad_weight(dyt_op, saved_xt, self.cfg)
         dx_partial = grad_input(dy_op, w_shard, self.cfg)
         if self.world == 1:
             return dx_partial, grad_weight(dyt_op, saved_xt, self.cfg)
