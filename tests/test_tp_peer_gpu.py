@@ -82,3 +82,36 @@ def test_peer_slot_reduce_scatter_matches_nccl(tmp_path):
     for r, (p, out) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, f"rank {r} failed:\n{out[-3000:]}"
         assert f"rank {r} ok" in out
+
+
+@pytest.mark.skipif(not torch.cuda.is_available(), reason="needs a GPU")
+@pytest.mark.parametrize("world", [2, 4])
+def test_scatter_epilogue_and_slot_sum_on_one_gpu(world):
+    """The ranks of a column-parallel dX emulated one after the other on one GPU: every "rank" runs the
+    scatter-mode GEMM on its shard with all slot buffers in local memory; the slot sums must equal the
+    sum of the plain GEMMs' outputs (same bf16 partials, fp32 sum), row block by row block."""
+    from triton_int8_b200 import _lib as L
+    from triton_int8_b200 import kernels as K
+    dev = "cuda"
+    M, Kd, N = 128 * world * 2, 384, 256 * world
+    g = torch.Generator().manual_seed(11)
+    dy = (torch.randn(M, N, generator=g) * 1e-2).bfloat16().to(dev)
+    w = (torch.randn(N, Kd, generator=g) * 0.05).bfloat16().to(dev)
+    rows = M // world
+    bufs = [torch.zeros(world, rows, Kd, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    ptrs = [b.data_ptr() for b in bufs]
+    partials = []
+    for r in range(world):
+        lo, hi = r * (N // world), (r + 1) * (N // world)
+        dyq, dys, _, _ = K.quant_tile(dy[None, :, lo:hi].contiguous())
+        wtq, wts = K.quant_col_t(w[lo:hi].contiguous())
+        partials.append(K.gemm_block(dyq, wtq, dys, wts)[0])
+        K.gemm_block_scatter(dyq, wtq, dys, wts, ptrs, r)
+    torch.cuda.synchronize()
+    for o in range(world):
+        for r in range(world):   # slot r of owner o holds rank r's rows of block o, bit for bit
+            assert torch.equal(bufs[o][r], partials[r][o * rows:(o + 1) * rows]), (o, r)
+        want = torch.stack([p[o * rows:(o + 1) * rows].float() for p in partials]).sum(0).to(torch.bfloat16)
+        assert torch.equal(K.sum_slots(bufs[o]), want)
+    with pytest.raises(L.I8LError):   # M must split into 128-row multiples per rank
+        K.gemm_block_scatter(dyq[:, :128], wtq, dys[:, :1], wts, ptrs, 0)
