@@ -73,6 +73,39 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
   return r;
 }
 
+// Packed fp32 pairs (one issue slot for two IEEE operations).  a - b is fma(b, -1, a): one rounding,
+// the same result as a subtraction.
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 sub2(float2 a, float2 b) { return __ffma2_rn(b, make_float2(-1.f, -1.f), a); }
+
+// Two values at once: the multiply and the +0.5 stay separate roundings, as in quant1.
+template <int MODE>
+__device__ __forceinline__ void quant2(float2 v, float2 s2, int& q0, int& q1) {
+  float2 y = __fmul2_rn(v, s2);
+  if (MODE == I8L_QMODE_RNE) {
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q0) : "f"(y.x));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q1) : "f"(y.y));
+    q0 = max(q0, -127);
+    q1 = max(q1, -127);
+  } else {
+    y = __fadd2_rn(y, make_float2(0.5f, 0.5f));
+    asm("cvt.rmi.sat.s8.f32 %0, %1;" : "=r"(q0) : "f"(y.x));
+    asm("cvt.rmi.sat.s8.f32 %0, %1;" : "=r"(q1) : "f"(y.y));
+  }
+}
+
+// Eight bf16 (a 16-byte piece) -> eight int8 in two words.
+template <int MODE>
+__device__ __forceinline__ uint2 quant_piece(const uint4& u, float s) {
+  const float2 s2 = make_float2(s, s);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+  int q[8];
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    quant2<MODE>(make_float2(__uint_as_float(w[k] << 16), __uint_as_float(w[k] & 0xffff0000u)), s2, q[2 * k], q[2 * k + 1]);
+  return make_uint2(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]));
+}
+
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t b) { return __uint_as_float(b << 16); }
 
 __device__ __forceinline__ void unpack8(const uint4& u, float* v) {

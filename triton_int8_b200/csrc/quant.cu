@@ -237,31 +237,36 @@ quant_tile_hadcols_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int
   for (int it = 0; it < 2; ++it) {
     const int r = 16 * w + 8 * it + rq;
     const __nv_bfloat16* xr = x + boff + (r_base + r) * cols + c_base;
-    float v[4][8];
+    float2 pv[4][4];  // piece c, pair k = elements 2k, 2k+1 of the piece
 #pragma unroll
-    for (int c = 0; c < 4; ++c) unpack8(__ldg(reinterpret_cast<const uint4*>(xr + 8 * (4 * c + j4))), v[c]);
-    // spans 1, 2, 4: inside a piece
+    for (int c = 0; c < 4; ++c) {
+      float v[8];
+      unpack8(__ldg(reinterpret_cast<const uint4*>(xr + 8 * (4 * c + j4))), v);
+      // span 1: inside each pair
 #pragma unroll
-    for (int c = 0; c < 4; ++c)
+      for (int k = 0; k < 4; ++k) pv[c][k] = make_float2(__fadd_rn(v[2 * k], v[2 * k + 1]), __fsub_rn(v[2 * k], v[2 * k + 1]));
+      // spans 2, 4: between the pairs of a piece, two butterflies per packed operation
 #pragma unroll
-      for (int h = 1; h < 8; h <<= 1)
+      for (int h = 1; h < 4; h <<= 1)
 #pragma unroll
-        for (int t = 0; t < 8; ++t)
-          if ((t & h) == 0) {
-            const float a = v[c][t], b = v[c][t | h];
-            v[c][t] = __fadd_rn(a, b);
-            v[c][t | h] = __fsub_rn(a, b);
+        for (int k = 0; k < 4; ++k)
+          if ((k & h) == 0) {
+            const float2 a = pv[c][k], b = pv[c][k | h];
+            pv[c][k] = add2(a, b);
+            pv[c][k | h] = sub2(a, b);
           }
-    // spans 8, 16: across the quad (element index = 32c + 8j + t)
+    }
+    // spans 8, 16: across the quad (element index = 32c + 8j + t): partner - own or own + partner
 #pragma unroll
     for (int m = 1; m < 4; m <<= 1) {
-      const bool upper = (j4 & m) != 0;
+      const float sg = (j4 & m) ? -1.f : 1.f;
+      const float2 sg2 = make_float2(sg, sg);
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int t = 0; t < 8; ++t) {
-          const float o = __shfl_xor_sync(0xffffffffu, v[c][t], m);
-          v[c][t] = upper ? __fsub_rn(o, v[c][t]) : __fadd_rn(v[c][t], o);
+        for (int k = 0; k < 4; ++k) {
+          const float2 o = make_float2(__shfl_xor_sync(0xffffffffu, pv[c][k].x, m), __shfl_xor_sync(0xffffffffu, pv[c][k].y, m));
+          pv[c][k] = __ffma2_rn(pv[c][k], sg2, o);   // exact products by +-1: own + partner, or partner - own
         }
     }
     // spans 32, 64: across the four pieces of the lane
@@ -271,21 +276,22 @@ quant_tile_hadcols_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int
       for (int c = 0; c < 4; ++c)
         if ((c & h) == 0)
 #pragma unroll
-          for (int t = 0; t < 8; ++t) {
-            const float a = v[c][t], b = v[c | h][t];
-            v[c][t] = __fadd_rn(a, b);
-            v[c | h][t] = __fsub_rn(a, b);
+          for (int k = 0; k < 4; ++k) {
+            const float2 a = pv[c][k], b = pv[c | h][k];
+            pv[c][k] = add2(a, b);
+            pv[c | h][k] = sub2(a, b);
           }
-    float m = 0.f;
+    __nv_bfloat162 hm = __floats2bfloat162_rn(0.f, 0.f);
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed[it][c]);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        h2[k] = __floats2bfloat162_rn(v[c][2 * k], v[c][2 * k + 1]);
-        m = fmaxf(m, fmaxf(fabsf(__low2float(h2[k])), fabsf(__high2float(h2[k]))));
+        h2[k] = __floats2bfloat162_rn(pv[c][k].x, pv[c][k].y);
+        hm = __hmax2(hm, __habs2(h2[k]));
       }
     }
+    float m = fmaxf(__low2float(hm), __high2float(hm));
     if (GRAN == I8L_GRAN_GROUP128) {
       m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
       m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
@@ -313,14 +319,7 @@ quant_tile_hadcols_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int
     const float s = GRAN == I8L_GRAN_TILE128 ? s_tile : s_row[it];
     int8_t* qr = q + boff + (r_base + r) * cols + c_base;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      float v[8];
-      unpack8(packed[it][c], v);
-      uint2 o;
-      o.x = pack4(quant1<MODE>(v[0], s), quant1<MODE>(v[1], s), quant1<MODE>(v[2], s), quant1<MODE>(v[3], s));
-      o.y = pack4(quant1<MODE>(v[4], s), quant1<MODE>(v[5], s), quant1<MODE>(v[6], s), quant1<MODE>(v[7], s));
-      *reinterpret_cast<uint2*>(qr + 8 * (4 * c + j4)) = o;
-    }
+    for (int c = 0; c < 4; ++c) *reinterpret_cast<uint2*>(qr + 8 * (4 * c + j4)) = quant_piece<MODE>(packed[it][c], s);
   }
 }
 
@@ -354,27 +353,38 @@ quant_tile_hadrows_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int
     }
   __syncthreads();
   const int c = tid >> 1, h = tid & 1;
-  float v[64];
+  float2 pv[32];  // pair k = rows 64h + 2k, 64h + 2k + 1 of column c
 #pragma unroll
-  for (int k = 0; k < 64; ++k) v[k] = s_tile[(64 * h + k) * LD + c];
+  for (int k = 0; k < 32; ++k) {  // span 1 on the way in
+    const float a = s_tile[(64 * h + 2 * k) * LD + c], b = s_tile[(64 * h + 2 * k + 1) * LD + c];
+    pv[k] = make_float2(__fadd_rn(a, b), __fsub_rn(a, b));
+  }
 #pragma unroll
-  for (int span = 1; span < 64; span <<= 1) {
+  for (int span = 1; span < 32; span <<= 1) {  // spans 2..32 of the elements: two butterflies per packed operation
 #pragma unroll
-    for (int k = 0; k < 64; ++k) {
+    for (int k = 0; k < 32; ++k) {
       if ((k & span) == 0) {
-        const float a = v[k], b = v[k | span];
-        v[k] = __fadd_rn(a, b);
-        v[k | span] = __fsub_rn(a, b);
+        const float2 a = pv[k], b = pv[k | span];
+        pv[k] = add2(a, b);
+        pv[k | span] = sub2(a, b);
       }
     }
   }
-  float m = 0.f;
+  // span 64: the partner lane holds the other half of the column; then round to bf16 as the
+  // reference's rotation does
+  uint32_t hv[32];
+  __nv_bfloat162 hm = __floats2bfloat162_rn(0.f, 0.f);
+  const float sg = h ? -1.f : 1.f;
+  const float2 sg2 = make_float2(sg, sg);
 #pragma unroll
-  for (int k = 0; k < 64; ++k) {  // span 64: partner lane holds the other half of the column
-    const float o = __shfl_xor_sync(0xffffffffu, v[k], 1);
-    v[k] = round_to_bf16(h ? __fsub_rn(o, v[k]) : __fadd_rn(v[k], o));
-    m = fmaxf(m, fabsf(v[k]));
+  for (int k = 0; k < 32; ++k) {
+    const float2 o = make_float2(__shfl_xor_sync(0xffffffffu, pv[k].x, 1), __shfl_xor_sync(0xffffffffu, pv[k].y, 1));
+    const float2 r = __ffma2_rn(pv[k], sg2, o);  // own + partner, or partner - own
+    const __nv_bfloat162 b2 = __floats2bfloat162_rn(r.x, r.y);
+    hm = __hmax2(hm, __habs2(b2));
+    hv[k] = *reinterpret_cast<const uint32_t*>(&b2);
   }
+  float m = fmaxf(__low2float(hm), __high2float(hm));
   float s, stored;
   if (GRAN == I8L_GRAN_TILE128) {
 #pragma unroll
@@ -400,13 +410,10 @@ quant_tile_hadrows_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int
   }
   int8_t* out = qt + boff + (c_base + c) * rows + r_base + 64 * h;
 #pragma unroll
-  for (int k = 0; k < 64; k += 16) {
-    uint4 o;
-    o.x = pack4(quant1<MODE>(v[k], s), quant1<MODE>(v[k + 1], s), quant1<MODE>(v[k + 2], s), quant1<MODE>(v[k + 3], s));
-    o.y = pack4(quant1<MODE>(v[k + 4], s), quant1<MODE>(v[k + 5], s), quant1<MODE>(v[k + 6], s), quant1<MODE>(v[k + 7], s));
-    o.z = pack4(quant1<MODE>(v[k + 8], s), quant1<MODE>(v[k + 9], s), quant1<MODE>(v[k + 10], s), quant1<MODE>(v[k + 11], s));
-    o.w = pack4(quant1<MODE>(v[k + 12], s), quant1<MODE>(v[k + 13], s), quant1<MODE>(v[k + 14], s), quant1<MODE>(v[k + 15], s));
-    *reinterpret_cast<uint4*>(out + k) = o;
+  for (int k = 0; k < 32; k += 8) {
+    const uint2 lo = quant_piece<MODE>(make_uint4(hv[k], hv[k + 1], hv[k + 2], hv[k + 3]), s);
+    const uint2 hi = quant_piece<MODE>(make_uint4(hv[k + 4], hv[k + 5], hv[k + 6], hv[k + 7]), s);
+    *reinterpret_cast<uint4*>(out + 2 * k) = make_uint4(lo.x, lo.y, hi.x, hi.y);
   }
 }
 
