@@ -65,6 +65,7 @@ struct GemmParams {
   // [world, rs_rows, N] bf16 buffer of rank o (peer memory), at slot rs_rank
   void* c_slots[I8L_MAX_RANKS];
   int rs_rows, rs_rank;
+  int m_rot;  // 128-row blocks by which the tile order is rotated (0 unless scattering)
   float post_scale;
 };
 
@@ -362,7 +363,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       tc.m_blk = 2 * tc.m_blk + (int)cluster_ctarank();
       return tc;
     } else {
-      return tile_coord(t, p.m_blocks, p);
+      TileCoord tc = tile_coord(t, p.m_blocks, p);
+      tc.m_blk += p.m_rot;  // scatter mode: every rank starts at a different owner's rows (no incast)
+      if (tc.m_blk >= p.m_blocks) tc.m_blk -= p.m_blocks;
+      return tc;
     }
   };
   const int KB = p.KB;
@@ -1012,6 +1016,10 @@ extern "C" int i8l_gemm_block_scatter(const int8_t* a_q, const int8_t* b_q, cons
   p.c = c_slots[rank];
   p.rs_rows = (int)(M / world);
   p.rs_rank = rank;
+  // All ranks walk the row blocks in the same order; starting rank r at the rows of rank r+1 keeps the
+  // ranks on different owners at any time (with eight ranks all writing to the same owner the dX GEMM
+  // took 5.3 ms instead of 2.5 ms).
+  p.m_rot = (int)(((rank + 1) % world) * (M / world / 128));
   return launch_gemm(true, a_q, b_q, p, 1, M, N, K, static_cast<cudaStream_t>(stream));
 }
 
