@@ -36,6 +36,7 @@ WORKLOADS = {
     "c1": (512, 1024, 1024, "config-1 512x1024x1024 block_channel fwd+dX+dW"),
     "c2": (8192, 4096, 4096, "config-2 double_channel forward M=8192 K=4096 N=4096 (full Hadamard, bias)"),
     "c2sq8192": (8192, 8192, 8192, "double_channel forward 8192^3 (full Hadamard)"),
+    "c5dc": (32768, 8192, 28672, "llama70b-mlp M=32768 K=8192 N=28672 double_channel fwd+dX+dW (per-row scales, whole-K int32 accumulation, no rotation)"),
 }
 NOMINAL_INT8_TOPS = 4500.0  # B200 dense INT8 datasheet figure
 
@@ -252,6 +253,34 @@ def main():
 
     ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
     gemm_events = []
+
+    if args.workload == "c5dc":
+        # The same linear layer with the double_channel scaling: three whole-K GEMMs (no per-128-K promotion).
+        if world > 1:
+            raise SystemExit("the double_channel workloads are single-GPU")
+        from triton_int8_b200.linear import Int8Config, linear_backward, linear_forward
+        dcfg = Int8Config(scaling="double_channel", hadamard=0)
+
+        def dcl_step():
+            y, saved = linear_forward(x, w, None, dcfg)
+            dx, dw = linear_backward(dy, w, saved, dcfg)
+            return y, dx, dw
+        for _ in range(max(args.warmup, 3)):
+            dcl_step()
+        torch.cuda.synchronize()
+        t0, t1 = ev(), ev()
+        t0.record()
+        for _ in range(args.steps):
+            dcl_step()
+        t1.record(); torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1) / args.steps
+        print(json.dumps({
+            "metric": "linear_fwd_bwd_tokens_per_s", "value": M / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": desc, "M": M, "K": K, "N": N},
+            "avg_tops_incl_quantizers": 6.0 * M * N * K / ms / 1e9, "gpu_launches": 9 * args.steps}))
+        return
 
     if args.workload.startswith("c2"):
         # double_channel forward only (BASELINE config 2): one step = rotate+quantize X per token,

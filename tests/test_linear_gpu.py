@@ -100,3 +100,38 @@ def test_llama7b_layer_shapes_chain_small_tokens():
         assert R.calc_diff(y.detach().float(), x.detach().float() @ w.t()) < 1e-3
         assert R.calc_diff(x.grad.float(), dy.float() @ w) < 1e-3
         assert R.calc_diff(lin.weight.grad.float(), dy.float().t() @ x.detach().float()) < 1e-3
+
+
+@pytest.mark.parametrize("had", [0, 128, -1])
+def test_linear_double_channel_matches_oracle_composition(had):
+    """scaling='double_channel': Y, dX and dW are the reference's double_channel product
+    (triton/double-channle_fwd32.py:295-311) applied to (X, W), (dY, W^T) and (dY^T, X^T)."""
+    from triton_int8_b200.linear import Int8Config, linear_backward, linear_forward
+    M, Kd, N = 256, 512, 1024
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(M, Kd, generator=g).to(torch.bfloat16)
+    x[:, ::61] *= 20
+    w = (torch.randn(N, Kd, generator=g) * 0.02).to(torch.bfloat16)
+    dy = (torch.randn(M, N, generator=g) * 1e-3).to(torch.bfloat16)
+    bias = (torch.randn(N, generator=g) * 0.01).to(torch.bfloat16)
+
+    def ref(a, b, with_bias=None):   # a [R, C], b [S, C] -> [R, S]
+        if had == 128:
+            aq, a_s = R.quant_row(R.hadamard(a[None], 128))
+            bq, b_s = R.quant_row(R.hadamard(b, 128))
+            c = R.gemm_rowcol(aq, bq, a_s, b_s).to(torch.bfloat16) * (1.0 / 128)
+        else:
+            c = R.double_channel_fwd_32(a[None], b, use_hadamard=had == -1)
+        c = c[0]
+        if with_bias is not None:   # bf16 result, then the bias added in fp32 and rounded again
+            c = (c.float() + with_bias.float()).to(torch.bfloat16)
+        return c
+
+    cfg = Int8Config(scaling="double_channel", hadamard=had)
+    y, saved = linear_forward(x.to(DEV), w.to(DEV), bias.to(DEV), cfg)
+    dx, dw = linear_backward(dy.to(DEV), w.to(DEV), saved, cfg)
+    assert torch.equal(y.cpu(), ref(x, w, bias))
+    assert torch.equal(dx.cpu(), ref(dy, w.t().contiguous()))
+    assert torch.equal(dw.cpu(), ref(dy.t().contiguous(), x.t().contiguous()))
+    exact = dy.float() @ w.float()
+    assert R.rel_fro(dx.cpu().float(), exact) < 5e-2

@@ -23,8 +23,11 @@ from . import kernels as K
 
 @dataclass(frozen=True)
 class Int8Config:
-    """scaling: 'tile128' (reference block_channel) or 'row128' (one scale per row and 128
-    contraction elements); round: 'half_up' (reference) or 'rne'; hadamard: 0 or 128 (rotate both
+    """scaling: 'tile128' (reference block_channel), 'row128' (one scale per row and 128
+    contraction elements) or 'double_channel' (one scale per row of each operand over the whole
+    contraction axis, int32 accumulation over all of it: triton/double-channle_fwd32.py:295-311 applied
+    to Y, dX and dW; hadamard may then also be -1 = rotate over the whole contraction axis, which must be
+    a power of two <= 32768); round: 'half_up' (reference) or 'rne'; hadamard: 0 or 128 (rotate both
     operands of every GEMM in 128-wide groups along that GEMM's contraction axis: K for Y, N for dX,
     the tokens for dW; each product is rescaled by 1/128);
     exact: reproduce the reference's fp32 operation order bit for bit (slower)."""
@@ -35,7 +38,7 @@ class Int8Config:
 
     @property
     def gran(self) -> int:
-        return {"tile128": L.GRAN_TILE128, "row128": L.GRAN_GROUP128}[self.scaling]
+        return {"tile128": L.GRAN_TILE128, "row128": L.GRAN_GROUP128, "double_channel": L.GRAN_ROW}[self.scaling]
 
     @property
     def qmode(self) -> int:
@@ -57,6 +60,16 @@ class Int8Config:
     def post(self) -> float:
         return 1.0 / self.hadamard if self.hadamard else 1.0
 
+    @property
+    def whole_k(self) -> bool:
+        return self.scaling == "double_channel"
+
+    def post_for(self, contraction: int) -> float:
+        """Rescale that undoes the rotation of both operands: 1/128, or 1/length for a whole-axis rotation."""
+        if not self.hadamard:
+            return 1.0
+        return 1.0 / contraction if self.hadamard == L.HAD_FULL else 1.0 / self.hadamard
+
 
 DEFAULT = Int8Config()
 
@@ -64,6 +77,8 @@ DEFAULT = Int8Config()
 def linear_forward(x2: torch.Tensor, weight: torch.Tensor, bias, cfg: Int8Config = DEFAULT, want_xt: bool = True):
     """x2 bf16 [M, K], weight bf16 [N, K] -> (y bf16 [M, N], saved) where saved holds the int8 X^T
     operand for dW (or None when want_xt is False)."""
+    if cfg.whole_k:
+        return _dc_forward(x2, weight, bias, cfg, want_xt)
     fuse_t = want_xt and not cfg.hadamard
     xq, xs, xqt, xst = K.quant_tile(x2[None], cfg.gran, cfg.qmode, cfg.hadamard, natural=True, transposed=fuse_t)
     if want_xt and not fuse_t:  # the dW operand X^T is rotated along the tokens, not along K: second pass over X
@@ -73,9 +88,26 @@ def linear_forward(x2: torch.Tensor, weight: torch.Tensor, bias, cfg: Int8Config
     return y, (xqt, xst)
 
 
+def _dc_forward(x2, weight, bias, cfg: Int8Config, want_xt: bool):
+    """double_channel forward: per-token and per-output-channel scales over all of K."""
+    Kd = x2.shape[1]
+    xq, xs = K.quant_row(x2[None], L.QMODE_ROWRCP, cfg.hadamard)
+    wq, ws = K.quant_row(weight, L.QMODE_ROWRCP, cfg.hadamard)
+    y = K.gemm_rowcol(xq, wq, xs, ws, bias, cfg.post_for(Kd))[0]
+    saved = (None, None)
+    if want_xt:   # dW operand: X^T [K, M], one scale per input feature over all tokens
+        xtq, xts = K.quant_row(x2.t().contiguous()[None], L.QMODE_ROWRCP, cfg.hadamard)
+        saved = (xtq, xts)
+    return y, saved
+
+
 def quantize_grad_output(dy2: torch.Tensor, cfg: Int8Config = DEFAULT, need_dx: bool = True, need_dw: bool = True):
     """One pass over dY [M, N] that yields the dX operand (dY, groups along N) and the dW operand
     (dY^T, groups along M).  Returns ((dyq, dys), (dyqt, dyst)); a pair not requested is (None, None)."""
+    if cfg.whole_k:
+        dy_op = K.quant_row(dy2[None], L.QMODE_ROWRCP, cfg.hadamard) if need_dx else (None, None)
+        dyt_op = K.quant_row(dy2.t().contiguous()[None], L.QMODE_ROWRCP, cfg.hadamard) if need_dw else (None, None)
+        return dy_op, dyt_op
     fuse_t = need_dw and not cfg.hadamard
     dyq, dys, dyqt, dyst = K.quant_tile(dy2[None], cfg.gran, cfg.qmode, cfg.hadamard,
                                         natural=need_dx, transposed=fuse_t)
@@ -87,6 +119,9 @@ def quantize_grad_output(dy2: torch.Tensor, cfg: Int8Config = DEFAULT, need_dx: 
 def grad_input(dy_op, weight: torch.Tensor, cfg: Int8Config = DEFAULT) -> torch.Tensor:
     """dX = dY W, bf16 [M, K]; W^T is quantised per input channel."""
     dyq, dys = dy_op
+    if cfg.whole_k:   # W^T [K, N], one scale per input channel over all of N
+        wtq, wts = K.quant_row(weight.t().contiguous(), L.QMODE_ROWRCP, cfg.hadamard)
+        return K.gemm_rowcol(dyq, wtq, dys, wts, None, cfg.post_for(weight.shape[0]))[0]
     wtq, wts = K.quant_col_t(weight, cfg.qmode, cfg.hadamard)   # rotated along N when hadamard is on
     return K.gemm_block(dyq, wtq, dys, wts, cfg.a_kind, L.BSCALE_CHANNEL, None, cfg.post, cfg.flags)[0]
 
@@ -94,6 +129,8 @@ def grad_input(dy_op, weight: torch.Tensor, cfg: Int8Config = DEFAULT) -> torch.
 def grad_weight(dyt_op, saved_xt, cfg: Int8Config = DEFAULT) -> torch.Tensor:
     """dW = dY^T X, bf16 [N, K], both operands scaled in groups along M."""
     (dyqt, dyst), (xqt, xst) = dyt_op, saved_xt
+    if cfg.whole_k:
+        return K.gemm_rowcol(dyqt, xqt, dyst, xst, None, cfg.post_for(dyqt.shape[-1]))[0]
     return K.gemm_block(dyqt, xqt, dyst, xst, cfg.a_kind, cfg.bt_kind, None, cfg.post, cfg.flags)[0]
 
 
