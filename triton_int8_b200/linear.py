@@ -88,6 +88,16 @@ def linear_forward(x2: torch.Tensor, weight: torch.Tensor, bias, cfg: Int8Config
     return y, (xqt, xst)
 
 
+def _dc_transposed(t2: torch.Tensor, cfg: Int8Config):
+    """t2 bf16 [R, C] -> (int8 t2^T [1, C, R], fp32 scale [1, C]): one scale per column of t2 over all rows.
+    Without rotation the transposing quantizer does it in one pass; a rotation along R goes through a
+    transposed copy and the row quantizer."""
+    if not cfg.hadamard:
+        q, s = K.quant_col_t(t2, L.QMODE_ROWRCP)
+        return q[None], s[None]
+    return K.quant_row(t2.t().contiguous()[None], L.QMODE_ROWRCP, cfg.hadamard)
+
+
 def _dc_forward(x2, weight, bias, cfg: Int8Config, want_xt: bool):
     """double_channel forward: per-token and per-output-channel scales over all of K."""
     Kd = x2.shape[1]
@@ -96,8 +106,7 @@ def _dc_forward(x2, weight, bias, cfg: Int8Config, want_xt: bool):
     y = K.gemm_rowcol(xq, wq, xs, ws, bias, cfg.post_for(Kd))[0]
     saved = (None, None)
     if want_xt:   # dW operand: X^T [K, M], one scale per input feature over all tokens
-        xtq, xts = K.quant_row(x2.t().contiguous()[None], L.QMODE_ROWRCP, cfg.hadamard)
-        saved = (xtq, xts)
+        saved = _dc_transposed(x2, cfg)
     return y, saved
 
 
@@ -106,7 +115,7 @@ def quantize_grad_output(dy2: torch.Tensor, cfg: Int8Config = DEFAULT, need_dx: 
     (dY^T, groups along M).  Returns ((dyq, dys), (dyqt, dyst)); a pair not requested is (None, None)."""
     if cfg.whole_k:
         dy_op = K.quant_row(dy2[None], L.QMODE_ROWRCP, cfg.hadamard) if need_dx else (None, None)
-        dyt_op = K.quant_row(dy2.t().contiguous()[None], L.QMODE_ROWRCP, cfg.hadamard) if need_dw else (None, None)
+        dyt_op = _dc_transposed(dy2, cfg) if need_dw else (None, None)
         return dy_op, dyt_op
     fuse_t = need_dw and not cfg.hadamard
     dyq, dys, dyqt, dyst = K.quant_tile(dy2[None], cfg.gran, cfg.qmode, cfg.hadamard,
@@ -120,8 +129,8 @@ def grad_input(dy_op, weight: torch.Tensor, cfg: Int8Config = DEFAULT) -> torch.
     """dX = dY W, bf16 [M, K]; W^T is quantised per input channel."""
     dyq, dys = dy_op
     if cfg.whole_k:   # W^T [K, N], one scale per input channel over all of N
-        wtq, wts = K.quant_row(weight.t().contiguous(), L.QMODE_ROWRCP, cfg.hadamard)
-        return K.gemm_rowcol(dyq, wtq, dys, wts, None, cfg.post_for(weight.shape[0]))[0]
+        wtq, wts = _dc_transposed(weight, cfg)
+        return K.gemm_rowcol(dyq, wtq[0], dys, wts[0], None, cfg.post_for(weight.shape[0]))[0]
     wtq, wts = K.quant_col_t(weight, cfg.qmode, cfg.hadamard)   # rotated along N when hadamard is on
     return K.gemm_block(dyq, wtq, dys, wts, cfg.a_kind, L.BSCALE_CHANNEL, None, cfg.post, cfg.flags)[0]
 
