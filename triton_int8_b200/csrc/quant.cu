@@ -223,7 +223,7 @@ quant_tile_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t col
 // stages cross lanes (spans 8 and 16); spans 1-4 and 32-64 run in registers.
 // ------------------------------------------------------------------------------------------------
 template <int GRAN, int MODE>
-__global__ void __launch_bounds__(256, 3)
+__global__ void __launch_bounds__(256, 4)
 quant_tile_hadcols_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t cols,
                           int8_t* __restrict__ q, float* __restrict__ scale) {
   __shared__ float s_red[8];
