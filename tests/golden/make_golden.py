@@ -1,7 +1,7 @@
 """Generate golden vectors by EXECUTING the reference's own Triton kernels on CPU.
 
-Run once, in a container that has the reference checkout (default /root/reference,
-override with I8L_REFERENCE_DIR) and triton installed:
+Run once, in a container that has the reference checkout (its path in I8L_REFERENCE_DIR)
+and triton installed:
 
     python tests/golden/make_golden.py
 
@@ -31,7 +31,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 from golden_inputs import make_inputs  # noqa: E402
 
-REF = os.environ.get("I8L_REFERENCE_DIR", "/root/reference")
+REF = os.environ.get("I8L_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
 
 
 def _load(name, rel):
