@@ -14,9 +14,15 @@
 // into fp32 registers (acc += float(P) * scale); in row x column mode a buffer holds a whole tile
 // and the epilogue of tile i overlaps the main loop of tile i+1.
 //
-// Every wait on an mbarrier is bounded in wall time; on expiry the CTA raises a shared abort flag,
-// reports through the status word and every role leaves its loop, so the kernel always terminates
-// and frees its tensor memory.
+// Every wait on an mbarrier is bounded (a poll count worth about two seconds); on expiry the CTA raises
+// a shared abort flag and reports through the status word.  The producer and the MMA issuer then leave
+// their loops; the epilogue warps, which meet at named barriers, run through their remaining tiles
+// without waiting or computing; copies in flight are awaited, so the kernel always terminates and
+// frees its tensor memory.
+//
+// Scatter mode (i8l_gemm_block_scatter): the epilogue writes each 128-row block into a slot of a
+// buffer owned by another GPU (plain stores to peer-mapped memory), for a reduce-scatter without a
+// separate collective kernel.
 #include <cuda.h>
 
 #include <cstdlib>
