@@ -129,6 +129,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   *abort_flag = 1;
   return false;
 }
+// The same bound for a caller that cannot leave its loop: returns when the phase has completed, or after
+// the limit with the abort flag set; once the flag is set (by any warp) a wait gives up after one poll.
+template <bool HINT = false>
+__device__ __forceinline__ void mbar_wait_or_flag(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait<HINT>(bar, parity)) return;
+  for (uint32_t spin = 1; spin < WAIT_MAX_POLLS; ++spin) {
+    if (*abort_flag) return;
+    if (mbar_try_wait<HINT>(bar, parity)) return;
+  }
+  *abort_flag = 1;
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -523,16 +534,17 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int d = 0; d < dn; ++d) {
             float f;
             asm volatile("ld.shared.f32 %0, [%1];" : "=f"(f) : "r"(fac0 + 4 * d));
-            // no early exit: a loop with one exit keeps the 64 accumulators where they are; after a
-            // timeout the remaining K blocks are skipped without further waits
-            ok = ok && mbar_wait(tfull0 + 8 * ab, aph, abort_flag);
+            // No early exit and no success flag: a loop with one exit and nothing to carry but the
+            // accumulators compiles to the leanest code.  After a timeout the abort flag is set, the status
+            // word reports it, and the remaining K blocks run on whatever tensor memory holds.
+            mbar_wait_or_flag(tfull0 + 8 * ab, aph, abort_flag);
             tc_fence_after();
             auto release = [&]() {  // all of this warp's tensor-memory loads of the buffer have completed
               tc_fence_before();
               __syncwarp();
               if (lane0) mbar_arrive(tempty0 + 8 * ab);
             };
-            if (ok && active) {
+            if (active) {
               const uint32_t taddr = taddr0 + ab * BN;
               const float2 f2 = make_float2(f, f);
 #pragma unroll
@@ -557,7 +569,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (ab == 0) aph ^= 1u;
           }
         }
-        if (ok && active) {
+        if (active) {
           int t2 = t;
           asm volatile("" : "+r"(t2));  // keeps the tile's coordinates out of the K-block loop's live registers
           const TileCoord tc = unit_tile(t2);
