@@ -283,6 +283,8 @@ __device__ __forceinline__ void st_global_256(void* ptr, const uint32_t* w) {
 // Final rescale, bias, cast and store of one thread's EPI_COLS consecutive columns.  Every lane of
 // a warp writes a different row, so each store instruction touches 32 lines: 32-byte stores (whole
 // sectors, half as many instructions) are used when the output pointer allows them.
+// POST = false: the caller has already folded post_scale into the scales it passes.
+template <bool POST = true>
 __device__ __forceinline__ void store_cols(const GemmParams& p, const float* acc, const float* bscale_or_null,
                                            int64_t row, int col0, void* cbase) {
 #pragma unroll
@@ -292,8 +294,11 @@ __device__ __forceinline__ void store_cols(const GemmParams& p, const float* acc
     for (int j = 0; j < 16; ++j) {
       v[j] = acc[j0 + j];
       if (bscale_or_null) v[j] *= bscale_or_null[j0 + j];
-      if (p.post_scale != 1.f) v[j] = __fmul_rn(v[j], p.post_scale);
-      if (p.bias) v[j] = __fadd_rn(v[j], __bfloat162float(p.bias[col0 + j0 + j]));
+      if (POST && p.post_scale != 1.f) v[j] = __fmul_rn(v[j], p.post_scale);
+    }
+    if (p.bias) {  // a uniform branch: no predicated-off loads and adds when there is no bias
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = __fadd_rn(v[j], __bfloat162float(p.bias[col0 + j0 + j]));
     }
     if (p.out_f32) {
       float* o = static_cast<float*>(cbase) + row * p.N + col0 + j0;
@@ -524,11 +529,12 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             active = col0 < p.N;
             const int64_t bcol0 = (int64_t)(p.b_batched ? tc.m_blk / p.mpb : 0) * p.N + col0;
             named_sync(1 + wg, 128);  // the group is done with the previous contents
-            if (k0 == 0 && chan && tix < EPI_COLS) ctl.bscale[wg][tix] = active ? __ldg(p.b_scale + bcol0 + tix) : 0.f;
+            if (k0 == 0 && chan && tix < EPI_COLS)  // post_scale rides on the column scale (on the factors otherwise)
+              ctl.bscale[wg][tix] = active ? __ldg(p.b_scale + bcol0 + tix) * p.post_scale : 0.f;
             const float* as_ptr = p.a_scale + (int64_t)tc.m_blk * KB + k0;
             const float* bs_ptr = p.b_scale + (bcol0 >> 7) * KB + k0;
             for (int i = tix; i < dn; i += 128)
-              ctl.fac[wg][i] = __ldg(as_ptr + i) * ((!chan && active) ? __ldg(bs_ptr + i) : 1.f);
+              ctl.fac[wg][i] = __ldg(as_ptr + i) * ((!chan && active) ? __ldg(bs_ptr + i) * p.post_scale : 1.f);
             named_sync(1 + wg, 128);
           }
           for (int d = 0; d < dn; ++d) {
@@ -586,7 +592,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             cbase = p.c_slots[owner];
             row += (int64_t)(p.rs_rank - owner) * p.rs_rows;
           }
-          store_cols(p, out, chan ? ctl.bscale[wg] : nullptr, row, tc.n_tile * BN + wg * EPI_COLS, cbase);
+          store_cols<false>(p, out, chan ? ctl.bscale[wg] : nullptr, row, tc.n_tile * BN + wg * EPI_COLS, cbase);
         }
       }
     } else
