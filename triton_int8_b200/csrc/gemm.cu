@@ -352,7 +352,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctl.tfull[b]), 1);
-      mbar_init(smem_u32(&ctl.tempty[b]), (TWO ? 2 : 1) * EPI_WARPS);  // one arrival per epilogue warp (of both CTAs)
+      // arrivals that free an accumulator buffer: one per epilogue warp (of both CTAs of a pair); the fast
+      // block kernel lets every epilogue thread arrive for itself (no warp sync, no branch in its loop)
+      mbar_init(smem_u32(&ctl.tempty[b]), KIND == K_BLOCK_FAST ? EPI_WARPS * 32 : (TWO ? 2 : 1) * EPI_WARPS);
     }
     mbar_init(smem_u32(&ctl.done), 1);
     ctl.abort_flag = 0;
@@ -510,10 +512,11 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // Values derived from the thread index pass through an empty asm statement: the compiler then
       // keeps them in registers instead of recomputing them from the special register at every use
       // inside the K-block loop (which cost about 35 ALU instructions per warp and K block).
-      uint32_t taddr0 = tmem_base + lane_addr + wg * EPI_COLS, fac0 = smem_u32(&ctl.fac[wg][0]), lane0 = lane == 0;
-      asm volatile("" : "+r"(taddr0), "+r"(fac0), "+r"(lane0));
+      uint32_t taddr0 = tmem_base + lane_addr + wg * EPI_COLS, fac0 = smem_u32(&ctl.fac[wg][0]);
+      asm volatile("" : "+r"(taddr0), "+r"(fac0));
       const bool chan = p.b_kind == I8L_BSCALE_CHANNEL;
       constexpr int CH = 8;
+      uint32_t gstep = 0;
       // The loops below never exit early: the warps of a column group meet at named barriers, so after a
       // wait timeout (`ok` false) a warp runs through the remaining tiles without waiting or computing.
       for (int t = I8L_UNIT; t < total_tiles; t += I8L_N_UNITS) {
@@ -547,8 +550,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             auto release = [&]() {  // all of this warp's tensor-memory loads of the buffer have completed
               tc_fence_before();
-              __syncwarp();
-              if (lane0) mbar_arrive(tempty0 + 8 * ab);
+              mbar_arrive(tempty0 + 8 * ab);   // every thread arrives for itself: no warp sync, no branch
             };
             if (active) {
               const uint32_t taddr = taddr0 + ab * BN;
@@ -571,8 +573,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             } else {
               release();
             }
-            ab ^= 1;
-            if (ab == 0) aph ^= 1u;
+            ++gstep;  // buffer and phase from one running count of K blocks
+            ab = gstep & 1;
+            aph = (gstep >> 1) & 1u;
           }
         }
         if (active) {
