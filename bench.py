@@ -383,6 +383,9 @@ def main():
     def avg(i, j):
         return statistics.mean(e[i].elapsed_time(e[j]) for e in gemm_events)
     t_fwd, t_dx, t_dw = avg(0, 1), avg(2, 3), avg(4, 5)
+    if os.environ.get("I8L_BENCH_TRACE") and rank == 0:   # per-step GEMM times, for chasing outliers
+        for name, (i, j) in (("fwd", (0, 1)), ("dx", (2, 3)), ("dw", (4, 5))):
+            print(f"[bench] {name} ms per step: " + " ".join(f"{e[i].elapsed_time(e[j]):.2f}" for e in gemm_events), file=sys.stderr)
     ops = 2.0 * M * Nl * K
     tops = {"fwd": ops / t_fwd / 1e9, "dx": ops / t_dx / 1e9, "dw": ops / t_dw / 1e9}
     # quantizer bandwidth (HBM-bound kernels), timed alone
