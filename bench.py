@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the INT8 quantized-linear hot path (forward + dX + dW of one linear layer).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c5|c4|c3|c2|sq8192]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c5|c3|c2|c1|sq8192|c2sq8192|c5dc]
 
 Workload (default c5): the Llama-70B MLP shape M=32768 tokens, K=8192, N=28672, block_channel
 scaling, W column-sharded along N over the N GPUs (strong scaling); synthetic seeded data with the
@@ -136,16 +136,22 @@ class CpuReference:
         self.cores = os.cpu_count() or 1
         torch.set_num_threads(self.cores)
         g = torch.Generator().manual_seed(20260004)
-        x = torch.randn(sample, K, generator=g)
-        cols = torch.randperm(K, generator=g)[: -(-K * 5 // 1000)]
-        x[:, cols] *= 30.0
-        self.x = x.to(torch.bfloat16)
         self.w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
-        self.dy = (torch.randn(sample, N, generator=g) * 1e-3).to(torch.bfloat16)
+        self.set_sample(sample)
         t0 = time.perf_counter()
         self.wq, self.ws = R.quant_token(self.rot(self.w))
         self.wtq, self.wts = R.quant_token(self.rot(self.w.t().contiguous()))
         self.t_weight = time.perf_counter() - t0
+
+    def set_sample(self, sample):
+        """(Re)draw the token-dependent inputs for `sample` tokens."""
+        g = torch.Generator().manual_seed(20260005)
+        x = torch.randn(sample, self.K, generator=g)
+        cols = torch.randperm(self.K, generator=g)[: -(-self.K * 5 // 1000)]
+        x[:, cols] *= 30.0
+        self.x = x.to(torch.bfloat16)
+        self.dy = (torch.randn(sample, self.N, generator=g) * 1e-3).to(torch.bfloat16)
+        self.Ms = sample
 
     def tokens_step(self):
         R = self.R
@@ -169,22 +175,48 @@ class CpuReference:
                 f"[{self.N},{self.K}] once; extrapolated linearly in tokens")
 
 
+def reference_sample_tokens(M, steps, warmup, s_per_token, budget_s=150.0):
+    """Tokens per sample step such that steps + warmup steps of the CPU port end within about budget_s,
+    given the seconds per token measured on this host: a multiple of 128 in [512, min(M, 8192)]."""
+    per_step = budget_s / max(1, steps + warmup)
+    return int(max(512, min(M, 8192, (per_step / s_per_token) // 128 * 128)))
+
+
+def workload_config(desc, had, M, K, N, world, **extra):
+    cfg = {"workload": desc, "hadamard": had, "M": M, "K": K, "N": N, "N_per_gpu": N // world,
+           "parallelism": f"tp{world}-column"}
+    cfg.update(extra)
+    return cfg
+
+
 def run_reference_arm(args, M, K, N, desc, had):
+    """The reference's path on the host cores: the CPU port of its semantics (oracle/), all host threads.
+    One step = the token-dependent work (quantise X and dY, three GEMMs with rescale) on a bounded sample of
+    the workload's tokens; the weight-only work is timed once on the full W.  `value` extrapolates to the
+    whole workload linearly in the token count; `ms_per_step` is the measured time of one sample step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    warm = min(args.warmup, 2)
     ref = CpuReference(M, K, N, min(M, 512), had)
-    for _ in range(min(args.warmup, 1)):
+    ref.tokens_step()                                     # first touch, then one calibration step
+    sample = reference_sample_tokens(M, args.steps, warm, ref.tokens_step() / ref.Ms)
+    ref.set_sample(sample)
+    for _ in range(warm):
         ref.tokens_step()
-    n = max(1, min(args.steps, 5))
-    t_tok = statistics.median([ref.tokens_step() for _ in range(n)])
+    times = [ref.tokens_step() for _ in range(args.steps)]
+    t_tok = statistics.median(times)
     v = ref.tokens_per_s(t_tok)
+    world = max(1, args.gpus)
     print(json.dumps({
         "impl": "reference", "metric": "linear_fwd_bwd_tokens_per_s", "value": v, "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * M / v,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": warm, "ms_per_step": 1e3 * t_tok,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": desc, "timing": "host perf_counter; torch CPU int8 matmul; see cpu_baseline.sample"},
-        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": ref.cores, "kind": "port", "sample": ref.describe(n),
+        "extrapolated": True, "sample_tokens_per_step": sample,
+        "ms_per_step_is": "one sample step of sample_tokens_per_step tokens (measured); value = M / (t_weight + t_step * M / sample)",
+        "config": workload_config(desc, had, M, K, N, world,
+                                  timing="host perf_counter; torch CPU int8 matmul, all host threads; runs on the host whatever --gpus says"),
+        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": ref.cores, "kind": "port", "sample": ref.describe(len(times)),
                          "t_weight_s": ref.t_weight, "t_tokens_s": t_tok},
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -367,49 +399,95 @@ def main():
             gemm_events.append(e)
         return y, dx, dw
 
-    # One GPU: the step (10 launches) is captured once into a CUDA graph and replayed, so that a host that
-    # is slow to issue launches (these machines are shared; stalls of 40-180 ms inside single steps were
-    # seen) cannot leave the GPU idle inside the timed region.  The per-GEMM event times come from the same
-    # step run launch by launch right afterwards.  Several GPUs: launch by launch (the collective and its
-    # side stream stay outside a capture).
+    # The step (10 launches, plus the reduce-scatter when sharded) is captured once into a CUDA graph and the
+    # timed region replays it, at every GPU count alike: a host that is slow to issue launches (these machines
+    # are shared; stalls of 40-180 ms inside single steps were seen) then cannot leave the GPU idle inside the
+    # timed region, and 1 GPU and 8 GPUs are timed in the same mode.  The same K steps are timed launch by
+    # launch right afterwards (`launch_by_launch`, with the per-GEMM events).  If the capture fails on any rank
+    # all ranks fall back to launch by launch.
+    def timed(run_one, n):
+        t0, t1 = ev(), ev()
+        sync_all()
+        t0.record()
+        for _ in range(n):
+            run_one()
+        t1.record()
+        sync_all()
+        t = t0.elapsed_time(t1)
+        if world > 1:
+            tms = torch.tensor([t], device=dev)
+            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+            t = tms.item()
+        return t / n
+
     graph, launch_mode = None, "launch by launch"
-    t0, t1 = ev(), ev()
     with ClockSampler(local_rank) as clk:
         for _ in range(max(args.warmup, 3)):
-            step()
+            out = step()
         sync_all()
-        if world == 1 and args.graph:
+        if args.graph:
             try:
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph):
                     out = step()
                 graph.replay()
                 torch.cuda.synchronize()
-                launch_mode = "CUDA graph replay of the whole step"
             except Exception as exc:  # noqa: BLE001 - capture is an optimisation of the harness, not of the step
-                print(f"[bench] graph capture failed ({exc!r}); timing launch by launch", file=sys.stderr)
+                print(f"[bench] rank {rank}: graph capture failed ({exc!r}); timing launch by launch", file=sys.stderr)
                 graph = None
                 torch.cuda.synchronize()
-        t0.record()
-        for _ in range(args.steps):
-            if graph is not None:
-                graph.replay()
-            else:
-                out = step(record=True)
-        t1.record()
-        sync_all()
+            if world > 1:   # all ranks must replay, or none
+                flag = torch.tensor([1.0 if graph is not None else 0.0], device=dev)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                if flag.item() == 0.0:
+                    graph = None
+        ms_graph = None
         if graph is not None:
-            for _ in range(args.steps):
-                out = step(record=True)
-            sync_all()
-    ms = t0.elapsed_time(t1)
-    if world > 1:
-        tms = torch.tensor([ms], device=dev)
-        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-        ms = tms.item()
-    ms_per_step = ms / args.steps
+            launch_mode = "CUDA graph replay of the whole step"
+            ms_graph = timed(graph.replay, args.steps)
+        ms_lbl = timed(lambda: step(record=True), args.steps)
+    ms_per_step = ms_graph if ms_graph is not None else ms_lbl
     tokens_per_s = M / (ms_per_step * 1e-3)
-    del out
+
+    # ---- parity of this very run (outside the timed region, every GPU count): one more step, its outputs
+    # against fp32 products of the same operands.  Y: 256 rows of this rank's columns; dX: the first 128 rows
+    # this rank owns after the reduce-scatter against the sum over ranks of dY_r[rows] W_r (fp32 partials,
+    # all-reduced); dW: a 128 x 256 block against dY_r^T X over all tokens.  calc_diff is the reference's own
+    # acceptance measure (triton/block_channel_fwd32.py:244-248, gate 1e-3).
+    def calc_diff(u, v):
+        u, v = u.double(), v.double()
+        return float(1 - 2 * (u * v).sum() / (u * u + v * v).sum())
+
+    def rel_fro(u, v):
+        return float((u.double() - v.double()).norm() / v.double().norm())
+
+    y, dx, dw = step()
+    sync_all()
+    Kn.check_status(dev)
+    rows_y = slice(0, 256)
+    y_ref = x[rows_y].float() @ w.float().t()
+    own0 = rank * (M // world)
+    rows_dx = slice(own0, own0 + 128)
+    dx_ref = dy[rows_dx].float() @ w.float()
+    if world > 1:
+        dist.all_reduce(dx_ref)
+    dw_ref = dy[:, :128].float().t() @ x[:, :256].float()
+    par = {"y": (y[0, rows_y] if y.dim() == 3 else y[rows_y], y_ref),
+           "dx": (dx[:128], dx_ref), "dw": (dw[:128, :256], dw_ref)}
+    parity = {}
+    for name, (got, ref_) in par.items():
+        parity[name] = {"calc_diff": calc_diff(got, ref_), "rel_fro": rel_fro(got, ref_)}
+    # Gates: the reference's 1e-3 for Y and dX.  dW gets 5e-3 on this workload: its operand X^T carries the
+    # outlier channels as rows, which a 128 x 128 tile scale cannot isolate (the CPU restatement of the
+    # reference gives the same 1.8e-3 on this data; tests/test_configs_gpu.py holds the GPU to that figure).
+    gates = {"y": 1e-3, "dx": 1e-3, "dw": 5e-3}
+    worst = torch.tensor([max(parity[k]["calc_diff"] / gates[k] for k in gates)], device=dev)
+    if world > 1:
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    parity["worst_calc_diff_over_gate_over_ranks"] = worst.item()
+    parity["gate"] = {"what": "calc_diff vs the fp32 product of the same bf16 operands, on every rank", **gates}
+    parity["ok"] = bool(worst.item() < 1.0)
+    del out, y, dx, dw, y_ref, dx_ref, dw_ref, par
 
     # per-GEMM device times inside the timed region (same stream as the launches)
     def avg(i, j):   # median over the steps: an interval also contains any host delay before the launch
@@ -446,7 +524,8 @@ def main():
     peaks, peak_src = measured_peaks()
     # INT8 tensor peak: MEASURED_PEAKS.json has no INT8 entry, so the cuBLAS int8 GEMM (torch._int_mm,
     # a library kernel used only as the measuring stick) is timed here on 8192^3: best single launch
-    # (burst) and back to back for ~1.5 s (sustained: the B200 sits at its 1000 W power cap there).
+    # (burst) and back to back for ~4 s (sustained: the B200 sits at its 1000 W power cap there), the same
+    # protocol as the bf16 figures of MEASURED_PEAKS.json.
     def cublas_int8_peak():
         n = 8192
         a8 = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=dev)
@@ -460,27 +539,61 @@ def main():
             a_.record(); torch._int_mm(a8, b8); b_.record(); torch.cuda.synchronize()
             best = min(best, a_.elapsed_time(b_))
         a_, b_ = ev(), ev()
-        reps = int(1500.0 / best)
+        reps = int(4000.0 / best)
         a_.record()
         for _ in range(reps):
             torch._int_mm(a8, b8)
         b_.record(); torch.cuda.synchronize()
         return 2.0 * n ** 3 / best / 1e9, 2.0 * n ** 3 / (a_.elapsed_time(b_) / reps) / 1e9
+    # The north-star target shape, isolated: one 8192^3 block_channel forward GEMM (tile x channel scales,
+    # fused rescale + bf16 store), best single launch and 20 launches back to back, before the sustained-peak
+    # loop heats the part.
+    def sq8192_block_fwd():
+        n = 8192
+        g8 = torch.Generator(device=dev).manual_seed(5)
+        a8 = torch.randn(1, n, n, device=dev, generator=g8).to(torch.bfloat16)
+        w8 = (torch.randn(n, n, device=dev, generator=g8) * 0.02).to(torch.bfloat16)
+        aq, a_s, _, _ = Kn.quant_tile(a8)
+        wq8, ws8 = Kn.quant_row(w8)
+        run = lambda: Kn.gemm_block(aq, wq8, a_s, ws8)  # noqa: E731
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(10):
+            a_, b_ = ev(), ev()
+            a_.record(); run(); b_.record(); torch.cuda.synchronize()
+            best = min(best, a_.elapsed_time(b_))
+        a_, b_ = ev(), ev()
+        a_.record()
+        for _ in range(20):
+            run()
+        b_.record(); torch.cuda.synchronize()
+        return 2.0 * n ** 3 / best / 1e9, 2.0 * n ** 3 / (a_.elapsed_time(b_) / 20) / 1e9
+    sq_best, sq_b2b = sq8192_block_fwd()
     int8_burst, int8_sustained = cublas_int8_peak()
+    targets = {"sq8192_block_fwd": {
+        "tops_best_launch": sq_best, "tops_20_back_to_back": sq_b2b,
+        "frac_of_cublas_int8_burst": sq_best / int8_burst,
+        "frac_of_2x_bf16_tflops_burst": sq_best / (2.0 * peaks["bf16_tflops"]),
+        "frac_of_nominal_4500": sq_best / NOMINAL_INT8_TOPS,
+        "what": "8192^3 block_channel forward GEMM alone (int8 operands resident, per-tile x per-channel rescale and bf16 store fused)"}}
     int8_peak = int8_sustained
     t_gemm = (t_fwd + t_dx + t_dw) / 3
-    traffic = None
+    traffic, traffic_per_gemm = None, None
     try:
         with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
             tr = json.load(f)["gemm_i8_kernel_block"]
             traffic = tr["dram_bytes_per_op"] * ops
+            traffic_per_gemm = {k: v * (1.0 / world) for k, v in tr.get("per_gemm_bytes_n1", {}).items()} or None
     except Exception:
         pass
     roofline = {
         "bound": "tensor", "kernel": "gemm_i8_kernel<block-scaled> (avg of Y, dX, dW launches)",
         "achieved": ops / t_gemm / 1e9, "peak": int8_peak, "unit": "TOP/s",
-        "frac": ops / t_gemm / 1e9 / int8_peak, "traffic": traffic,
-        "peak_source": "cuBLAS int8 GEMM (torch._int_mm) 8192^3 sustained for 1.5 s, measured in this run; "
+        "frac": ops / t_gemm / 1e9 / int8_peak, "traffic": traffic, "traffic_per_gemm": traffic_per_gemm,
+        "frac_of_2x_bf16_sustained": ops / t_gemm / 1e9 / (2.0 * peaks["bf16_tflops_sustained"]),
+        "peak_source": "cuBLAS int8 GEMM (torch._int_mm) 8192^3 sustained for 4 s, measured in this run; "
                        f"burst {int8_burst:.0f}; MEASURED_PEAKS.json ({peak_src}) has no INT8 entry, 2 x its bf16 sustained = "
                        f"{2.0 * peaks['bf16_tflops_sustained']:.0f}",
         "peak_burst": int8_burst,
@@ -536,24 +649,29 @@ def main():
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        ref = CpuReference(M, K, N, min(M, 512), had)
-        t_tok = statistics.median([ref.tokens_step() for _ in range(3)])
+        sample = 2048   # about 10 s per pass of the port on 16 cores
+        ref = CpuReference(M, K, N, min(M, sample), had)
+        t_tok = statistics.median([ref.tokens_step() for _ in range(2)])
         cpu_baseline = {"value": ref.tokens_per_s(t_tok), "unit": "tokens/s", "cores": ref.cores, "kind": "port",
-                        "sample": ref.describe(3), "t_weight_s": ref.t_weight, "t_tokens_s": t_tok}
+                        "sample": ref.describe(2), "t_weight_s": ref.t_weight, "t_tokens_s": t_tok, "extrapolated": True}
 
     if rank == 0:
         print(json.dumps({
             "metric": "linear_fwd_bwd_tokens_per_s", "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": desc, "hadamard": had, "M": M, "K": K, "N": N, "N_per_gpu": Nl, "parallelism": f"tp{world}-column", "reduce_scatter": rs_mode, "launch": launch_mode,
-                       "l2": "inputs (X 0.5 GB + dY >= 0.2 GB per step) exceed the 126 MB L2; no explicit flush"},
+            "config": workload_config(desc, had, M, K, N, world, reduce_scatter=rs_mode, launch=launch_mode,
+                                      l2="inputs (X 0.5 GB + dY >= 0.2 GB per step) exceed the 126 MB L2; no explicit flush"),
+            "launch_by_launch": {"ms_per_step": ms_lbl, "value": M / (ms_lbl * 1e-3)},
+            "parity": parity,
             "tops_per_gpu": tops, "gemm_ms": {"fwd": t_fwd, "dx": t_dx, "dw": t_dw},
-            "roofline": roofline, "quantizers": quant, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "roofline": roofline, "targets": targets, "quantizers": quant, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": launches_per_step * args.steps, "clocks": clk.summary(),
         }))
     if world > 1:
         dist.destroy_process_group()
+    if not parity["ok"]:
+        raise SystemExit(f"parity gate failed: {parity}")
 
 
 if __name__ == "__main__":

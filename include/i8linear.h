@@ -37,6 +37,8 @@ extern "C" {
 #define I8L_GRAN_TILE128 0  /* one scale per 128x128 tile            (reference block_channel A/dY) */
 #define I8L_GRAN_GROUP128 1 /* one scale per (row, 128 contraction elements)                        */
 #define I8L_GRAN_ROW 2      /* one scale per row over the whole contraction axis (per token/channel)*/
+#define I8L_GRAN_TILE128X256 5 /* one scale per 128 rows x 256 contraction elements (the activation
+                                  grouping of the reference's TileLang forward, tilelang/block_channel_fwd.py:185-188) */
 
 /* Arithmetic of scale and rounding.  x is bf16 widened to fp32, amax the group's max |x|. */
 #define I8L_QMODE_TRITON 0 /* amax=max(amax,1e-4); s=127/amax (IEEE); q=clamp(floor(x*s+.5),-128,127); stores 1/s.
@@ -47,6 +49,10 @@ extern "C" {
                               triton/fused_triton_fwd32.py:49-59, triton/fused_triton_bwd33.py:50-56 */
 #define I8L_QMODE_ROWRCP 3 /* s=rcp(max(amax,1e-4))*127; q=clamp(floor(x*s+.5),-128,127); stores amax/127.
                               triton/double-channle_fwd32.py:157-160,132-135 */
+
+#define I8L_QMODE_TRITON_BF16S 4 /* as TRITON, the stored 1/s rounded to bf16 (kept in an fp32 array): the
+                                    TileLang forward's quantizers write their scales to bf16 tensors and
+                                    widen them afterwards.  tilelang/block_channel_fwd.py:133,149,191,204 */
 
 /* Walsh-Hadamard rotation applied (in fp32, result rounded to bf16) before quantisation,
  * always along the contraction axis of the operand. */
@@ -62,6 +68,8 @@ extern "C" {
  *                  scale: TILE128 -> fp32 [batch, rows/128, cols/128]; GROUP128 -> [batch, rows, cols/128].
  *   qt / scale_t : the operand x^T (per batch), contraction axis = rows.  qt is int8 [batch, cols, rows].
  *                  scale_t: TILE128 -> [batch, cols/128, rows/128]; GROUP128 -> [batch, cols, rows/128].
+ * I8L_GRAN_TILE128X256 (scale fp32 [batch, rows/128, cols/256], cols a multiple of 256) produces q only,
+ * without rotation.
  * Either pair may be NULL (not produced).  hadamard is I8L_HAD_NONE or I8L_HAD_128; the rotation
  * always runs along the contraction axis of the operand it belongs to (cols for q, rows for qt), so
  * with a rotation the two operands come from two passes over x instead of one.
@@ -123,6 +131,8 @@ I8L_API int i8l_quant_col_t_static(const void* x, int64_t rows, int64_t cols, in
 /* Scale layouts understood by the GEMM. */
 #define I8L_ASCALE_TILE 0  /* a_scale fp32 [batch, M/128, K/128] */
 #define I8L_ASCALE_GROUP 1 /* a_scale fp32 [batch, M, K/128]     */
+#define I8L_ASCALE_TILE256 2 /* a_scale fp32 [batch, M/128, K/256]: one scale serves two consecutive K blocks
+                                (tilelang/block_channel_fwd.py:33,76); K a multiple of 256 */
 #define I8L_BSCALE_CHANNEL 0 /* b_scale fp32 [N]  (shared B) or [batch, N]      : K-invariant        */
 #define I8L_BSCALE_TILE 1    /* b_scale fp32 [N/128, K/128] or [batch, N/128, K/128]                  */
 #define I8L_BSCALE_GROUP 2   /* b_scale fp32 [N, K/128]     or [batch, N, K/128]                      */
@@ -134,6 +144,9 @@ I8L_API int i8l_quant_col_t_static(const void* x, int64_t rows, int64_t cols, in
                                   EXACT_ORDER a true division per element, otherwise a multiplication by the rounded
                                   reciprocal of a_s*b_s (differs from the division by at most 1 ulp per K block) */
 #define I8L_GEMM_OUT_F32 4     /* C is fp32 instead of bf16 */
+#define I8L_GEMM_PRODUCT_FIRST 8 /* with EXACT_ORDER: evaluate float(P) * (a_s*b_s) instead of (float(P)*a_s)*b_s per K
+                                    step, the order of the reference's TileLang kernels
+                                    (tilelang/block_channel_fwd.py:75-81, tilelang/block_channel_bwd.py:76-81) */
 
 /*
  * Block-scaled INT8 GEMM: for every 128-wide K block kb, P = A_q[:,kb] . B_q[:,kb]^T exactly in int32
@@ -197,6 +210,17 @@ I8L_API int i8l_gemm_block_scatter(const int8_t* a_q, const int8_t* b_q, const f
  * rounded once (deterministic).  cols a multiple of 8.  No counterpart in the reference.
  */
 I8L_API int i8l_sum_slots(const void* slots, void* out, int world, int64_t rows, int64_t cols, void* stream);
+
+/*
+ * Test hook for the bounded waits of the GEMM kernels (not for production use; process-wide until reset).
+ * Every wait on an mbarrier inside the GEMMs gives up after a number of polls (about two seconds' worth)
+ * and the kernel then returns with I8L_ERR_TIMEOUT in the caller's status word instead of hanging.
+ * max_polls > 0 lowers that limit for all following launches (0 restores the default);
+ * withhold_one_load != 0 makes the operand producer of every CTA leave out the last load of its first
+ * tile, so that the waits depending on it run into the limit.  Together they let a test see the timeout
+ * path end to end without a fault, a trap or an unbounded spin.  No counterpart in the reference.
+ */
+I8L_API int i8l_test_set_wait_limit(uint32_t max_polls, int withhold_one_load);
 
 /* Text of the calling thread's most recent error ("" if none). */
 I8L_API const char* i8l_last_error(void);

@@ -154,6 +154,120 @@ def quant_rowgroup128(x: torch.Tensor):
     return q, _div_true(1.0, s).reshape(*lead, K // BLK)
 
 
+def quant_rne_native(x: torch.Tensor, group: str):
+    """The torch helpers of tilelang/block_channel_fwd.py with their arithmetic kept in the INPUT dtype
+    (no upcast anywhere: for bf16 input the absmax, `127.0 / amax` = reciprocal * 127, the product
+    x * scale, round() and the returned 1.0 / scale are all bf16 operations, each rounded to bf16):
+      group "tile"     per 128x128 tile of x [B, M, K]       tilelang/block_channel_fwd.py:222-230
+      group "row"      per row of x [M, K]                   tilelang/block_channel_fwd.py:215-220
+      group "row128"   per (row, 128 columns) of x [M, K]    tilelang/block_channel_fwd.py:206-213 (commented out)
+    The copy in tilelang/block_channel_bwd.py:96-104 upcasts the absmax to fp32 first, which promotes
+    everything after it to fp32: that one is quant_tile128_rne above.  For fp32 input the two agree.
+    Returns (int8 like x, scale in x.dtype)."""
+    if group == "tile":
+        B, M, K = x.shape
+        v = x.reshape(B, M // BLK, BLK, K // BLK, BLK)
+        amax = v.abs().amax(dim=(2, 4), keepdim=True)
+        out_shape, s_shape = (B, M, K), (B, M // BLK, K // BLK)
+    elif group == "row":
+        M, K = x.shape
+        v = x
+        amax = v.abs().amax(dim=1, keepdim=True)
+        out_shape, s_shape = (M, K), (M, 1)
+    else:
+        M, K = x.shape
+        v = x.reshape(M, K // BLK, BLK)
+        amax = v.abs().amax(dim=2, keepdim=True)
+        out_shape, s_shape = (M, K), (M, K // BLK)
+    s = _rdiv_torch(127.0, amax.clamp(min=1e-4))
+    q = (v * s).round().clamp(-127, 127).to(torch.int8).reshape(out_shape)
+    return q, _rdiv_torch(1.0, s).reshape(s_shape)
+
+
+# --------------------------------------------------------------------------- TileLang variant numerics
+def _bf16_rne(t: torch.Tensor) -> torch.Tensor:
+    """fp32 -> bf16 (round to nearest even, what a GPU store does) -> fp32."""
+    return t.to(torch.bfloat16).float()
+
+
+def quant_tile128x256_bf16scale(x: torch.Tensor):
+    """Activation quantizer in front of the TileLang forward GEMM: one scale per 128 rows x 256
+    columns (tilelang/block_channel_fwd.py:185-188), live Triton arithmetic (true division, round
+    half up, no clamp: :168-172), the stored reciprocal scale rounded to bf16 because the wrapper
+    allocates a bf16 scale tensor and widens it afterwards (:191, :204).
+    x bf16 [B, M, K] (K a multiple of 256) -> int8 [B, M, K], fp32 scale [B, M/128, K/256].
+    Also returns the unrounded fp32 scale (what the kernel computes before the bf16 store)."""
+    B, M, K = x.shape
+    v = x.float().view(B, M // BLK, BLK, K // 256, 256)
+    amax = v.abs().amax(dim=(2, 4), keepdim=True)
+    amax = torch.where(amax > 1e-4, amax, torch.full_like(amax, 1e-4))
+    s = _div_true(127.0, amax)
+    q = _round_half_up_i8(v * s, False).view(B, M, K)
+    inv = _div_true(1.0, s).view(B, M // BLK, K // 256)
+    return q, _bf16_rne(inv), inv
+
+
+def quant_token_bf16scale(w: torch.Tensor):
+    """Per-row weight quantizer of the same file (tilelang/block_channel_fwd.py:94-121, bf16 scale
+    tensor :133, widened :149).  w bf16 [N, K] -> int8 [N, K], fp32 scale [N, 1] (+ unrounded scale)."""
+    v = w.float()
+    amax = v.abs().amax(dim=1, keepdim=True)
+    amax = torch.where(amax > 1e-4, amax, torch.full_like(amax, 1e-4))
+    s = _div_true(127.0, amax)
+    q = _round_half_up_i8(v * s, False)
+    inv = _div_true(1.0, s)
+    return q, _bf16_rne(inv), inv
+
+
+def gemm_tilelang_fwd(aq, bq, a_s, b_s) -> torch.Tensor:
+    """TileLang forward GEMM (tilelang/block_channel_fwd.py:66-83): per 128-wide K step the column
+    factor is the PRODUCT a_s[b, mb, (k*128)//256] * b_s[n] (:75-76), then
+    acc_f32[m, n] += float(P[m, n]) * factor[n] (:80-81), evaluated unfused (multiply, then add).
+    aq [B, M, K], bq [N, K], a_s [B, M/128, K/256], b_s [N] or [N, 1] -> fp32 [B, M, N]."""
+    B, M, K = aq.shape
+    N = bq.shape[0]
+    out = torch.zeros(B, M, N, dtype=torch.float32)
+    bs = b_s.reshape(1, N)
+    for b in range(B):
+        for kb in range(K // BLK):
+            P = int_mm(aq[b, :, kb * BLK:(kb + 1) * BLK], bq[:, kb * BLK:(kb + 1) * BLK]).float()
+            fac = a_s[b, :, (kb * BLK) // 256].repeat_interleave(BLK).view(M, 1) * bs
+            out[b] += P * fac
+    return out
+
+
+def gemm_tilelang_bwd(aq, bq, a_s, b_s) -> torch.Tensor:
+    """TileLang backward GEMM (tilelang/block_channel_bwd.py:66-83): scalar factor
+    a_s[b, mb, kb] * b_s[b, nb, kb] per tile and K step (:76), acc += float(P) * factor (:80-81).
+    aq [B, M, K], bq [B, N, K], fp32 scales per 128x128 tile -> fp32 [B, M, N]."""
+    B, M, K = aq.shape
+    N = bq.shape[1]
+    out = torch.zeros(B, M, N, dtype=torch.float32)
+    for b in range(B):
+        for kb in range(K // BLK):
+            P = int_mm(aq[b, :, kb * BLK:(kb + 1) * BLK], bq[b, :, kb * BLK:(kb + 1) * BLK]).float()
+            fac = a_s[b, :, kb].repeat_interleave(BLK).view(M, 1) * b_s[b, :, kb].repeat_interleave(BLK).view(1, N)
+            out[b] += P * fac
+    return out
+
+
+def tilelang_fwd_32(a: torch.Tensor, b: torch.Tensor, return_fp32: bool = False):
+    """tilelang/block_channel_fwd.py:271-292 (quantizers :277-278, GEMM :287-288)."""
+    aq, a_s, _ = quant_tile128x256_bf16scale(a)
+    bq, b_s, _ = quant_token_bf16scale(b)
+    c = gemm_tilelang_fwd(aq, bq, a_s, b_s)
+    return c if return_fp32 else c.to(torch.bfloat16)
+
+
+def tilelang_bwd_33(a: torch.Tensor, b: torch.Tensor, return_fp32: bool = False):
+    """tilelang/block_channel_bwd.py:197-223: both operands per 128x128 tile with fp32 scales
+    (:141-157, the clamp-less kernel), scale product first."""
+    aq, a_s = quant_tile128(a, clamp=False)
+    bq, b_s = quant_tile128(b, clamp=False)
+    c = gemm_tilelang_bwd(aq, bq, a_s, b_s)
+    return c if return_fp32 else c.to(torch.bfloat16)
+
+
 # --------------------------------------------------------------------------- Hadamard
 def hadamard(x: torch.Tensor, block: int | None = None) -> torch.Tensor:
     """Un-normalised Walsh-Hadamard transform (Sylvester order) along the last dim.

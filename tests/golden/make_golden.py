@@ -31,7 +31,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 from golden_inputs import make_inputs  # noqa: E402
 
-REF = os.environ.get("I8L_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
+REF = os.environ.get("I8L_REFERENCE_DIR")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set I8L_REFERENCE_DIR to the checkout of the reference project")
 
 
 def _load(name, rel):
@@ -145,6 +147,93 @@ def fused(case):
     return dict(c_fwd=C, c_bwd=C2)
 
 
+def _extract(rel, names, uncomment=None):
+    """Source text of the named top-level functions of a reference file, without importing the file
+    (the TileLang files need a tilelang version that is not installed).  `uncomment` = (first, last)
+    1-based line range of a commented-out function whose leading "# " is stripped and which is
+    returned under the name `<name>_commented`."""
+    import ast
+    text = open(os.path.join(REF, rel)).read()
+    lines = text.splitlines()
+    out = []
+    for node in ast.parse(text).body:
+        if isinstance(node, ast.FunctionDef) and node.name in names:
+            first = min([node.lineno] + [d.lineno for d in node.decorator_list])
+            out.append("\n".join(lines[first - 1:node.end_lineno]))
+    if uncomment:
+        body = [l[2:] if l.startswith("# ") else l.lstrip("#") for l in lines[uncomment[0] - 1:uncomment[1]]]
+        body[0] = body[0].replace("def per_token_cast_to_int8", "def per_token_cast_to_int8_commented")
+        out.append("\n".join(body))
+    return "\n\n".join(out)
+
+
+def _module_from_source(name, source):
+    """Import extracted source through a temporary file (triton.jit needs inspect.getsource to work)."""
+    import tempfile
+    d = tempfile.mkdtemp(prefix="i8l_golden_")
+    path = os.path.join(d, name + ".py")
+    with open(path, "w") as f:
+        f.write("import torch\nimport triton\nimport triton.language as tl\nfrom typing import Tuple\n\n" + source + "\n")
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def torch_helpers():
+    """The reference's pure-torch quantisation helpers, executed as they stand:
+    tilelang/block_channel_bwd.py:96-104 (tile 128x128, amax upcast to fp32),
+    tilelang/block_channel_fwd.py:215-230 (per row and per tile, arithmetic in the INPUT dtype) and the
+    commented-out per-(row, 128) version at tilelang/block_channel_fwd.py:206-213.  Each is run on the
+    bf16 inputs of the `small` and `edge` cases and on unrounded fp32 inputs."""
+    fwd = _module_from_source("ref_tl_fwd_helpers", _extract(
+        "tilelang/block_channel_fwd.py", {"per_token_cast_to_int8", "per_block_cast_to_int8"}, uncomment=(206, 213)))
+    bwd = _module_from_source("ref_tl_bwd_helpers", _extract("tilelang/block_channel_bwd.py", {"per_block_cast_to_int8"}))
+    out = {}
+    g = torch.Generator().manual_seed(20260110)
+    cases = {"small": make_inputs("small")[:2], "edge": make_inputs("edge")[:2],
+             "f32": (torch.randn(2, 256, 512, generator=g) * 3.0, torch.randn(384, 512, generator=g) * 0.02)}
+    for cname, (a, w) in cases.items():
+        for fname, fn, arg in (("bwd_block", bwd.per_block_cast_to_int8, a), ("fwd_block", fwd.per_block_cast_to_int8, a),
+                               ("fwd_token", fwd.per_token_cast_to_int8, w),
+                               ("fwd_group", fwd.per_token_cast_to_int8_commented, w)):
+            q, sc = fn(arg.clone())
+            out[f"{cname}__{fname}__q"] = q
+            out[f"{cname}__{fname}__s"] = sc.float()          # bf16 scales are stored widened (exact)
+            out[f"{cname}__{fname}__s_dtype"] = torch.tensor([{torch.float32: 32, torch.bfloat16: 16}[sc.dtype]])
+    return out
+
+
+def tilelang_quantizers():
+    """The Triton quantizers that feed the TileLang GEMM (tilelang/block_channel_fwd.py:94-121 per row,
+    :152-183 per 128x256 tile), run under the interpreter.  The wrappers allocate bf16 scale tensors
+    (:133, :191); the interpreter truncates on a bf16 store where a GPU rounds to nearest even, so the
+    kernels are launched here with fp32 scale tensors and the consumer applies the bf16 rounding."""
+    mod = _module_from_source("ref_tl_fwd_quant", _extract(
+        "tilelang/block_channel_fwd.py", {"per_token_quant_kernel", "per_block_quant_kernel"}))
+    out = {}
+    for cname in ("small", "edge"):
+        a, w, _ = make_inputs(cname)
+        B, M, K = a.shape
+        N = w.shape[0]
+        aq = torch.empty_like(a, dtype=torch.int8)
+        a_s = torch.empty((B, M // 128, K // 256), dtype=torch.float32)
+        mod.per_block_quant_kernel[(B * (M // 128) * (K // 256),)](
+            X_ptr=a, SCALE_ptr=a_s, OUT_ptr=aq, B=B, M=M, N=K,
+            stride_b=a.stride(0), stride_m=a.stride(1), stride_n=a.stride(2),
+            stride_sb=a_s.stride(0), stride_sm=a_s.stride(1), stride_sn=a_s.stride(2),
+            stride_ob=aq.stride(0), stride_om=aq.stride(1), stride_on=aq.stride(2),
+            BLOCK_M=128, BLOCK_N=256)
+        wq = torch.empty_like(w, dtype=torch.int8)
+        w_s = torch.empty((N, 1), dtype=torch.float32)
+        mod.per_token_quant_kernel[(N // 128, 1)](
+            X_ptr=w, SCALE_ptr=w_s, OUT_ptr=wq, M=N, N=K,
+            stride_xm=w.stride(0), stride_xn=w.stride(1), stride_sm=w_s.stride(0), stride_sn=w_s.stride(1),
+            stride_om=wq.stride(0), stride_on=wq.stride(1), BLOCK_M=128, BLOCK_N=K)
+        out.update({f"{cname}__aq": aq, f"{cname}__a_s_f32": a_s, f"{cname}__wq": wq, f"{cname}__w_s_f32": w_s})
+    return out
+
+
 def save(name, case, outs, digest_only=False):
     rec = {"case": np.array(case)}
     for k, v in outs.items():
@@ -158,8 +247,14 @@ def save(name, case, outs, digest_only=False):
 
 
 if __name__ == "__main__":
+    if "--helpers-only" in sys.argv:
+        save("torch_helpers", "small+edge+f32", torch_helpers())
+        save("tilelang_quantizers", "small+edge", tilelang_quantizers())
+        raise SystemExit(0)
     save("block_channel_small", "small", block_channel("small"))
     save("block_channel_edge", "edge", block_channel("edge"))
     save("double_channel_small", "dc_small", double_channel("dc_small"))
     save("fused_small", "small", fused("small"))
     save("block_channel_c1", "c1", block_channel("c1"), digest_only=True)
+    save("torch_helpers", "small+edge+f32", torch_helpers())
+    save("tilelang_quantizers", "small+edge", tilelang_quantizers())

@@ -280,3 +280,43 @@ def test_hadamard_along_tokens_for_transposed_operand(gran):
     xt_rot = R.hadamard(x.transpose(1, 2).contiguous(), 128)
     q_ref, s_ref = R.quant_tile128(xt_rot) if gran == "tile" else R.quant_rowgroup128(xt_rot)
     _same(qt, q_ref, "rotated transposed int8"); _same(st, s_ref, "rotated transposed scale")
+
+
+# ------------------------------------------------------------------------------ TileLang variant numerics
+@pytest.mark.parametrize("case", ["small", "edge"])
+def test_tilelang_variant_quantizers_and_gemm(golden_dir, case):
+    """scaling="tile128x256_bf16scale": activation scale per 128 x 256, scales rounded to bf16, scale
+    product first (tilelang/block_channel_fwd.py:33,75-81,185-204).  The quantizers are checked against
+    the reference's own Triton kernels (golden, unrounded scales + the bf16 rounding a GPU store applies),
+    the GEMM against the cited restatement."""
+    g = _golden(golden_dir, "tilelang_quantizers")
+    a, w, b3 = make_inputs(case)
+    aq, a_s = BC.triton_per_block256_quant(a.to(DEV))
+    wq, w_s = BC.triton_per_token_quant_bf16scale(w.to(DEV))
+    _same(aq, g[f"{case}__aq"], "128x256 int8"); _same(wq, g[f"{case}__wq"], "row int8")
+    _same(a_s, torch.as_tensor(g[f"{case}__a_s_f32"]).to(torch.bfloat16).float(), "128x256 scale (bf16-rounded)")
+    _same(w_s, torch.as_tensor(g[f"{case}__w_s_f32"]).to(torch.bfloat16).float(), "row scale (bf16-rounded)")
+    ref = R.tilelang_fwd_32(a, w, return_fp32=True)
+    got = BC.fwd_32(a.to(DEV), w.to(DEV), scaling="tile128x256_bf16scale", exact=True, out_dtype=torch.float32)
+    _same(got, ref, "TileLang forward numerics, exact order, fp32")
+    fast = BC.fwd_32(a.to(DEV), w.to(DEV), scaling="tile128x256_bf16scale")
+    assert R.rel_fro(fast.cpu().float(), ref) < TOL_BF16
+    ref_b = R.tilelang_bwd_33(a, b3, return_fp32=True)
+    got_b = BC.bwd_33(a.to(DEV), b3.to(DEV), scaling="tilelang_tile128", exact=True, out_dtype=torch.float32)
+    _same(got_b, ref_b, "TileLang backward numerics, exact order, fp32")
+    assert R.rel_fro(BC.bwd_33(a.to(DEV), b3.to(DEV), scaling="tilelang_tile128").cpu().float(), ref_b) < TOL_BF16
+
+
+def test_rowcol_fp32_output_applies_post_scale_and_bias():
+    """double_channel pipeline with an fp32 result: the 1/K rescale and the bias are applied in fp32
+    (the reference multiplies its GEMM output, whatever its type, by 1/K:
+    triton/double-channle_fwd32.py:284)."""
+    a, w, _ = make_inputs("dc_small")
+    bias = (torch.arange(w.shape[0], dtype=torch.float32) * 1e-3).to(torch.bfloat16)
+    for had in ("full", 128, None):
+        rot = (lambda t: R.hadamard(t)) if had == "full" else ((lambda t: R.hadamard(t, 128)) if had == 128 else (lambda t: t))
+        aq, a_s = R.quant_row(rot(a)); wq, w_s = R.quant_row(rot(w))
+        post = 1.0 / a.shape[-1] if had == "full" else (1.0 / 128 if had == 128 else 1.0)
+        ref = R.gemm_rowcol(aq, wq, a_s, w_s) * post + bias.float()
+        got = DC.int8_gemm_pipeline(a.to(DEV), w.to(DEV), out_dtype=torch.float32, hadamard=had, bias=bias.to(DEV))
+        _same(got, ref, f"fp32 double_channel pipeline, hadamard={had}")

@@ -14,12 +14,12 @@ LIB_PATH = os.environ.get("I8L_LIBRARY_PATH") or os.path.join(_PKG_DIR, "libi8li
 OK = 0
 ERR_NAMES = {-1: "SHAPE", -2: "ALIGN", -3: "ARCH", -4: "CUDA", -5: "TIMEOUT", -6: "ARG"}
 
-GRAN_TILE128, GRAN_GROUP128, GRAN_ROW = 0, 1, 2
-QMODE_TRITON, QMODE_RNE, QMODE_FUSED, QMODE_ROWRCP = 0, 1, 2, 3
+GRAN_TILE128, GRAN_GROUP128, GRAN_ROW, GRAN_TILE128X256 = 0, 1, 2, 5
+QMODE_TRITON, QMODE_RNE, QMODE_FUSED, QMODE_ROWRCP, QMODE_TRITON_BF16S = 0, 1, 2, 3, 4
 HAD_NONE, HAD_128, HAD_FULL = 0, 128, -1
-ASCALE_TILE, ASCALE_GROUP = 0, 1
+ASCALE_TILE, ASCALE_GROUP, ASCALE_TILE256 = 0, 1, 2
 BSCALE_CHANNEL, BSCALE_TILE, BSCALE_GROUP = 0, 1, 2
-GEMM_EXACT_ORDER, GEMM_DIVIDE, GEMM_OUT_F32 = 1, 2, 4
+GEMM_EXACT_ORDER, GEMM_DIVIDE, GEMM_OUT_F32, GEMM_PRODUCT_FIRST = 1, 2, 4, 8
 MAX_RANKS = 8
 
 _P, _I64, _I, _F = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float
@@ -35,6 +35,7 @@ SIGNATURES = {
     "i8l_gemm_dump_i32": [_P, _P, _I, _P, _I64, _I64, _I64, _I64, _I, _P, _P],
     "i8l_gemm_block_scatter": [_P, _P, _P, _P, _I, _F, _P, _I, _I, _I64, _I64, _I64, _P, _P],
     "i8l_sum_slots": [_P, _P, _I, _I64, _I64, _P],
+    "i8l_test_set_wait_limit": [ctypes.c_uint32, _I],
     "i8l_version": [],
 }
 

@@ -30,10 +30,11 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 template <int MODE>
 __device__ __forceinline__ void make_scale(float amax, float& s, float& stored) {
-  if (MODE == I8L_QMODE_TRITON) {
+  if (MODE == I8L_QMODE_TRITON || MODE == I8L_QMODE_TRITON_BF16S) {
     amax = amax > 1e-4f ? amax : 1e-4f;
     s = __fdiv_rn(127.0f, amax);
     stored = __fdiv_rn(1.0f, s);
+    if (MODE == I8L_QMODE_TRITON_BF16S) stored = __bfloat162float(__float2bfloat16_rn(stored));
   } else if (MODE == I8L_QMODE_RNE) {
     amax = fmaxf(amax, 1e-4f);
     s = __fmul_rn(__frcp_rn(amax), 127.0f);

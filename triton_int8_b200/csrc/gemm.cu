@@ -25,7 +25,7 @@
 // separate collective kernel.
 #include <cuda.h>
 
-#include <cstdlib>
+#include <atomic>
 #include <cstring>
 
 #include "common.cuh"
@@ -65,6 +65,8 @@ struct GemmParams {
   int M, N, KB;  // KB = K/128
   int a_kind, b_kind, b_batched;
   int exact, divide, out_f32, dump;  // dump: 0 none, 1 whole-K int32, 2 per-K-block int32
+  int a_kshift;       // an A tile scale serves 2^a_kshift consecutive K blocks (1 for 128x256 groups)
+  int product_first;  // exact order only: float(P) * (a_s*b_s) instead of (float(P)*a_s)*b_s
   int raster;
   int c_align32;  // the output pointer is 32-byte aligned: 256-bit stores
   // scatter mode (rs_rows > 0): rows [o*rs_rows, (o+1)*rs_rows) of the product go to c_slots[o], a
@@ -73,6 +75,8 @@ struct GemmParams {
   int rs_rows, rs_rank;
   int m_rot;  // 128-row blocks by which the tile order is rotated (0 unless scattering)
   float post_scale;
+  uint32_t max_polls;  // limit of every mbarrier wait, in polls (WAIT_MAX_POLLS unless a test lowers it)
+  int withhold;        // test hook: the producer leaves out the last operand load of its first tile
 };
 
 // ------------------------------------------------------------------------------------------ PTX
@@ -132,9 +136,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // The same bound for a caller that cannot leave its loop: returns when the phase has completed, or after
 // the limit with the abort flag set; once the flag is set (by any warp) a wait gives up after one poll.
 template <bool HINT = false>
-__device__ __forceinline__ void mbar_wait_or_flag(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ void mbar_wait_or_flag(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  uint32_t max_polls = WAIT_MAX_POLLS) {
   if (mbar_try_wait<HINT>(bar, parity)) return;
-  for (uint32_t spin = 1; spin < WAIT_MAX_POLLS; ++spin) {
+  for (uint32_t spin = 1; spin < max_polls; ++spin) {
     if (*abort_flag) return;
     if (mbar_try_wait<HINT>(bar, parity)) return;
   }
@@ -408,7 +413,12 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int a_row = tc.m_blk * BM;
         const int b_row = (p.b_batched ? (tc.m_blk / p.mpb) * p.N : 0) + tc.n_tile * BN + (TWO ? (int)rank * BM : 0);
         for (int kb = 0; kb < KB; ++kb) {
-          if (!(ok = mbar_wait<!BLOCK>(smem_u32(&ctl.empty[s]), ph ^ 1u, abort_flag))) break;
+          if (!(ok = mbar_wait<!BLOCK>(smem_u32(&ctl.empty[s]), ph ^ 1u, abort_flag, p.max_polls))) break;
+          if (p.withhold && t == I8L_UNIT && kb == KB - 1) {
+            // test hook: this stage is never filled, so the waits that depend on it run into their limit
+            if (++s == STAGES) { s = 0; ph ^= 1u; }
+            continue;
+          }
           if (lane == 0) {
             const uint32_t bar = smem_u32(&ctl.full[s]);
             if (TWO) {  // both CTAs' copies complete on the leader's barrier, which expects the bytes of both
@@ -446,11 +456,11 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           // block-scaled kinds wait for the accumulator buffer last (the epilogue's release is what holds
           // the next MMA up); the whole-K kinds measured 0.7 % faster the other way round
           if (!BLOCK && drain_start) {
-            if (!(ok = mbar_wait<!BLOCK>(smem_u32(&ctl.tempty[ab]), aph ^ 1u, abort_flag))) break;
+            if (!(ok = mbar_wait<!BLOCK>(smem_u32(&ctl.tempty[ab]), aph ^ 1u, abort_flag, p.max_polls))) break;
           }
-          if (!(ok = mbar_wait<!BLOCK>(smem_u32(&ctl.full[s]), ph, abort_flag))) break;
+          if (!(ok = mbar_wait<!BLOCK>(smem_u32(&ctl.full[s]), ph, abort_flag, p.max_polls))) break;
           if (BLOCK) {
-            if (!(ok = mbar_wait<!BLOCK>(smem_u32(&ctl.tempty[ab]), aph ^ 1u, abort_flag))) break;
+            if (!(ok = mbar_wait<!BLOCK>(smem_u32(&ctl.tempty[ab]), aph ^ 1u, abort_flag, p.max_polls))) break;
           }
           tc_fence_after();
           if (lane == 0) {
@@ -534,10 +544,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             named_sync(1 + wg, 128);  // the group is done with the previous contents
             if (k0 == 0 && chan && tix < EPI_COLS)  // post_scale rides on the column scale (on the factors otherwise)
               ctl.bscale[wg][tix] = active ? __ldg(p.b_scale + bcol0 + tix) * p.post_scale : 0.f;
-            const float* as_ptr = p.a_scale + (int64_t)tc.m_blk * KB + k0;
+            const float* as_ptr = p.a_scale + (int64_t)tc.m_blk * (KB >> p.a_kshift);
             const float* bs_ptr = p.b_scale + (bcol0 >> 7) * KB + k0;
             for (int i = tix; i < dn; i += 128)
-              ctl.fac[wg][i] = __ldg(as_ptr + i) * ((!chan && active) ? __ldg(bs_ptr + i) * p.post_scale : 1.f);
+              ctl.fac[wg][i] = __ldg(as_ptr + ((k0 + i) >> p.a_kshift)) * ((!chan && active) ? __ldg(bs_ptr + i) * p.post_scale : 1.f);
             named_sync(1 + wg, 128);
           }
           for (int d = 0; d < dn; ++d) {
@@ -546,7 +556,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // No early exit and no success flag: a loop with one exit and nothing to carry but the
             // accumulators compiles to the leanest code.  After a timeout the abort flag is set, the status
             // word reports it, and the remaining K blocks run on whatever tensor memory holds.
-            mbar_wait_or_flag(tfull0 + 8 * ab, aph, abort_flag);
+            mbar_wait_or_flag(tfull0 + 8 * ab, aph, abort_flag, p.max_polls);
             tc_fence_after();
             auto release = [&]() {  // all of this warp's tensor-memory loads of the buffer have completed
               tc_fence_before();
@@ -578,7 +588,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             aph = (gstep >> 1) & 1u;
           }
         }
-        if (active) {
+        if (active && !*abort_flag) {   // after a timeout the accumulators are not a product: nothing is stored
           int t2 = t;
           asm volatile("" : "+r"(t2));  // keeps the tile's coordinates out of the K-block loop's live registers
           const TileCoord tc = unit_tile(t2);
@@ -624,7 +634,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int d = 0; d < KB; ++d) {
           const float f = f_next;
           if (d + 1 < KB) f_next = __ldg(as_ptr + d + 1) * ((!chan && active) ? __ldg(bs_ptr + d + 1) : 1.f);
-          ok = ok && mbar_wait<!BLOCK>(smem_u32(&ctl.tfull[ab]), aph, abort_flag);  // single-exit loop, see K_BLOCK_FAST
+          ok = ok && mbar_wait<!BLOCK>(smem_u32(&ctl.tfull[ab]), aph, abort_flag, p.max_polls);  // single-exit loop, see K_BLOCK_FAST
           tc_fence_after();
           if (ok && active) {
             const uint32_t taddr = tmem_base + lane_addr + ab * BN + wg * EPI_COLS;
@@ -686,7 +696,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (tix < EPI_COLS) ctl.bstep[wg][d & 1][tix] = f;
             named_sync(1 + wg, 128);
           }
-          ok = ok && mbar_wait<!BLOCK>(smem_u32(&ctl.tfull[ab]), aph, abort_flag);  // single-exit loop, see K_BLOCK_FAST
+          ok = ok && mbar_wait<!BLOCK>(smem_u32(&ctl.tfull[ab]), aph, abort_flag, p.max_polls);  // single-exit loop, see K_BLOCK_FAST
           tc_fence_after();
           if (ok && active) {
             const uint32_t taddr = tmem_base + lane_addr + ab * BN + wg * EPI_COLS;
@@ -733,15 +743,15 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int d = 0; d < ndrain; ++d) {
           float sa = 1.f, sb = 1.f;
           if (BLOCK && !p.dump) {
-            sa = p.a_kind == I8L_ASCALE_TILE ? __ldg(p.a_scale + (int64_t)tc.m_blk * KB + d)
-                                             : __ldg(p.a_scale + row * KB + d);
+            sa = p.a_kind == I8L_ASCALE_GROUP ? __ldg(p.a_scale + row * KB + d)
+                                              : __ldg(p.a_scale + (int64_t)tc.m_blk * (KB >> p.a_kshift) + (d >> p.a_kshift));
             if (p.b_kind == I8L_BSCALE_TILE && active) sb = __ldg(p.b_scale + (bcol0 >> 7) * KB + d);
             if (p.b_kind == I8L_BSCALE_GROUP) {
               if (tix < EPI_COLS) ctl.bstep[wg][d & 1][tix] = active ? __ldg(p.b_scale + (bcol0 + tix) * KB + d) : 0.f;
               named_sync(1 + wg, 128);
             }
           }
-          ok = ok && mbar_wait<!BLOCK>(smem_u32(&ctl.tfull[ab]), aph, abort_flag);
+          ok = ok && mbar_wait<!BLOCK>(smem_u32(&ctl.tfull[ab]), aph, abort_flag, p.max_polls);
           tc_fence_after();
           const bool live = ok && active;
           const uint32_t taddr = tmem_base + lane_addr + ab * BN + wg * EPI_COLS;
@@ -771,6 +781,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                   const float sbj = sbv ? sbv[c * 16 + j] : sb;
                   float term;
                   if (p.divide) term = __fdiv_rn(pf, __fmul_rn(sa, sbj));
+                  else if (p.product_first) term = __fmul_rn(pf, __fmul_rn(sa, sbj));
                   else term = __fmul_rn(__fmul_rn(pf, sa), sbj);
                   acc[c * 16 + j] = __fadd_rn(acc[c * 16 + j], term);
                 }
@@ -787,8 +798,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 v[j] = __fmul_rn(__fmul_rn(__int2float_rn((int)r[j]), sar), ctl.bscale[wg][c * 16 + j]);
-                if (!p.out_f32 && (p.post_scale != 1.f || p.bias)) {
-                  v[j] = round_to_bf16(v[j]);  // the reference rounds to bf16 before its 1/K pass
+                if (p.post_scale != 1.f || p.bias) {
+                  // the reference stores the GEMM result in the output type before its 1/K pass: a bf16
+                  // rounding for bf16 outputs, none for fp32 ones
+                  if (!p.out_f32) v[j] = round_to_bf16(v[j]);
                   v[j] = __fmul_rn(v[j], p.post_scale);
                   if (p.bias) v[j] = __fadd_rn(v[j], __bfloat162float(p.bias[col0 + c * 16 + j]));
                 }
@@ -855,19 +868,38 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 static EncodeTiledFn get_encode() {
-  static EncodeTiledFn fn = nullptr;
+  static std::atomic<EncodeTiledFn> cached{nullptr};
+  EncodeTiledFn fn = cached.load(std::memory_order_acquire);
   if (!fn) {
     void* p = nullptr;
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
         qres == cudaDriverEntryPointSuccess)
       fn = reinterpret_cast<EncodeTiledFn>(p);
+    cached.store(fn, std::memory_order_release);
   }
   return fn;
 }
 
-// int8 [rows, K] row-major -> boxes of box_rows x 128 bytes, 128B swizzle.
+// int8 [rows, K] row-major -> boxes of box_rows x 128 bytes, 128B swizzle.  A tensor map depends only
+// on (pointer, rows, K, box rows); a training loop calls with the same few operands step after step, so
+// the last maps of each host thread are kept (no lock: the cache is thread local) and the driver's
+// encode call leaves the launch path.
+struct MapKey {
+  const void* ptr;
+  int64_t rows, K;
+  int box_rows;
+};
 static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box_rows) {
+  constexpr int SLOTS = 16;
+  thread_local MapKey keys[SLOTS] = {};
+  thread_local CUtensorMap maps[SLOTS];
+  thread_local int next_slot = 0;
+  for (int i = 0; i < SLOTS; ++i)
+    if (keys[i].ptr == ptr && keys[i].rows == rows && keys[i].K == K && keys[i].box_rows == box_rows) {
+      *map = maps[i];
+      return I8L_OK;
+    }
   EncodeTiledFn enc = get_encode();
   if (!enc) return fail(I8L_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -878,25 +910,39 @@ static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, 
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(I8L_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  keys[next_slot] = MapKey{ptr, rows, K, box_rows};
+  maps[next_slot] = *map;
+  next_slot = (next_slot + 1) % SLOTS;
   return I8L_OK;
 }
 
-static int sm_count() {
-  static int cached[64];
+constexpr int MAX_DEVICES = 64;
+static int current_device() {
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
-  if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
-  return cached[dev];
+  return (dev < 0 || dev >= MAX_DEVICES) ? 0 : dev;
 }
+
+static int sm_count() {
+  static std::atomic<int> cached[MAX_DEVICES];
+  const int dev = current_device();
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (!n) {
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cached[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
+// Test hooks (i8l_test_set_wait_limit): 0 = production values.
+static std::atomic<uint32_t> g_test_max_polls{0};
+static std::atomic<int> g_test_withhold{0};
 
 template <int KIND, bool TWO>
 static int launch_kind(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int64_t tiles, cudaStream_t st) {
-  static bool attr_set[64];
-  static int max_clusters[64];
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
+  // per-device set-up, done by whichever thread comes first (idempotent, so a race only repeats it)
+  static std::atomic<int> max_units[MAX_DEVICES];   // 0 = not set up yet
+  const int dev = current_device();
   auto kernel = gemm_i8_kernel<KIND, TWO>;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
@@ -911,30 +957,22 @@ static int launch_kind(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
     cfg.attrs = attr;
     cfg.numAttrs = 1;
   }
-  if (!attr_set[dev]) {
+  int units = max_units[dev].load(std::memory_order_acquire);
+  if (!units) {
     I8L_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_DYN));
+    units = sm_count();
     if (TWO) {  // how many CTA pairs can be co-resident (GPCs with an odd SM count leave one SM unpaired)
       cfg.gridDim = dim3(2 * sm_count(), 1, 1);
       int n = 0;
       I8L_CUDA_OK(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
-      max_clusters[dev] = n > 0 ? n : 1;
+      units = n > 0 ? n : 1;
     }
-    attr_set[dev] = true;
+    max_units[dev].store(units, std::memory_order_release);
   }
-  const int units = TWO ? max_clusters[dev] : sm_count();
   const int grid_units = (int)(tiles < units ? tiles : units);
   cfg.gridDim = dim3(TWO ? 2 * grid_units : grid_units, 1, 1);
   I8L_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, ma, mb, p));
   return I8L_OK;
-}
-
-static bool pair_mode_enabled() {  // development override: I8L_PAIR=0 forces one CTA per tile
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("I8L_PAIR");
-    v = (e && e[0] == '0') ? 0 : 1;
-  }
-  return v != 0;
 }
 
 static int launch_gemm(bool block, const int8_t* a_q, const int8_t* b_q, GemmParams p, int64_t batch, int64_t M,
@@ -951,7 +989,7 @@ static int launch_gemm(bool block, const int8_t* a_q, const int8_t* b_q, GemmPar
   // CTA pairs (cta_group::2) need two 128-row blocks of the same batch per tile.  They pay off for the
   // whole-K accumulation (half the B traffic per SM: +2.5 % sustained at the power cap); the per-K-block
   // hand-off of the block-scaled kinds is slower across two CTAs (990 vs 1510 TOP/s), so those stay 1-CTA.
-  const bool two = !block && pair_mode_enabled() && (M % 256 == 0);
+  const bool two = !block && (M % 256 == 0);
   CUtensorMap ma, mb;
   if (int e = make_map(&ma, a_q, batch * M, K, BM)) return e;
   if (int e = make_map(&mb, b_q, p.b_batched ? batch * N : N, K, two ? BM : BN)) return e;
@@ -961,6 +999,11 @@ static int launch_gemm(bool block, const int8_t* a_q, const int8_t* b_q, GemmPar
   p.M = (int)M;
   p.N = (int)N;
   p.KB = (int)(K / 128);
+  {
+    const uint32_t lim = g_test_max_polls.load(std::memory_order_relaxed);
+    p.max_polls = lim ? lim : WAIT_MAX_POLLS;
+    p.withhold = g_test_withhold.load(std::memory_order_relaxed);
+  }
   p.c_align32 = (reinterpret_cast<uintptr_t>(p.c) & 31u) == 0;
   for (int r = 0; r < I8L_MAX_RANKS; ++r)
     if (p.rs_rows && p.c_slots[r] && (reinterpret_cast<uintptr_t>(p.c_slots[r]) & 31u)) p.c_align32 = 0;
@@ -991,13 +1034,22 @@ extern "C" int i8l_gemm_block(const int8_t* a_q, const int8_t* b_q, const float*
                               void* c, int64_t batch, int64_t M, int64_t N, int64_t K, int flags, int32_t* status,
                               void* stream) {
   if (!a_scale || !b_scale) return fail(I8L_ERR_ARG, "null scale pointer");
-  if (a_scale_kind != I8L_ASCALE_TILE && a_scale_kind != I8L_ASCALE_GROUP) return fail(I8L_ERR_ARG, "bad a_scale_kind");
+  if (a_scale_kind != I8L_ASCALE_TILE && a_scale_kind != I8L_ASCALE_GROUP && a_scale_kind != I8L_ASCALE_TILE256)
+    return fail(I8L_ERR_ARG, "bad a_scale_kind");
+  if (a_scale_kind == I8L_ASCALE_TILE256 && (K % 256 || b_scale_kind != I8L_BSCALE_CHANNEL || (flags & I8L_GEMM_DIVIDE)))
+    return fail(I8L_ERR_ARG, "I8L_ASCALE_TILE256 needs K %% 256 == 0 and per-channel b scales");
+  if ((flags & I8L_GEMM_PRODUCT_FIRST) && !(flags & I8L_GEMM_EXACT_ORDER))
+    return fail(I8L_ERR_ARG, "I8L_GEMM_PRODUCT_FIRST selects an operation order: it needs I8L_GEMM_EXACT_ORDER");
   if (b_scale_kind < I8L_BSCALE_CHANNEL || b_scale_kind > I8L_BSCALE_GROUP) return fail(I8L_ERR_ARG, "bad b_scale_kind");
   if ((flags & I8L_GEMM_DIVIDE) && b_scale_kind == I8L_BSCALE_CHANNEL)
     return fail(I8L_ERR_ARG, "I8L_GEMM_DIVIDE needs per-K-block b scales");
   GemmParams p{};
   p.a_scale = a_scale; p.b_scale = b_scale; p.bias = static_cast<const __nv_bfloat16*>(bias); p.c = c;
-  p.status = status; p.a_kind = a_scale_kind; p.b_kind = b_scale_kind; p.b_batched = b_batched ? 1 : 0;
+  p.status = status; p.b_kind = b_scale_kind; p.b_batched = b_batched ? 1 : 0;
+  // 128x256 groups are per-tile scales indexed with a halved K-block number
+  p.a_kind = a_scale_kind == I8L_ASCALE_TILE256 ? I8L_ASCALE_TILE : a_scale_kind;
+  p.a_kshift = a_scale_kind == I8L_ASCALE_TILE256 ? 1 : 0;
+  p.product_first = (flags & I8L_GEMM_PRODUCT_FIRST) ? 1 : 0;
   p.exact = (flags & I8L_GEMM_EXACT_ORDER) ? 1 : 0;
   p.divide = (flags & I8L_GEMM_DIVIDE) ? 1 : 0;
   p.out_f32 = (flags & I8L_GEMM_OUT_F32) ? 1 : 0;
@@ -1057,9 +1109,16 @@ extern "C" int i8l_sum_slots(const void* slots, void* out, int world, int64_t ro
   if (int e = check_arch()) return e;
   const int64_t n16 = rows * cols / 8;
   const int64_t want = (n16 + 255) / 256;
-  const int grid = (int)(want < 148 * 8 ? want : 148 * 8);
+  const int64_t cap = (int64_t)sm_count() * 8;
+  const int grid = (int)(want < cap ? want : cap);
   sum_slots_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(slots),
                                                                         static_cast<uint4*>(out), world, n16);
   I8L_CUDA_OK(cudaGetLastError());
+  return I8L_OK;
+}
+
+extern "C" int i8l_test_set_wait_limit(uint32_t max_polls, int withhold_one_load) {
+  g_test_max_polls.store(max_polls, std::memory_order_relaxed);
+  g_test_withhold.store(withhold_one_load ? 1 : 0, std::memory_order_relaxed);
   return I8L_OK;
 }

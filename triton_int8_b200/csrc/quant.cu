@@ -1,5 +1,6 @@
 // bf16 -> int8 absmax quantizers (HBM-bound): 128x128-tile kernel with optional transposed
 // output and fused 128-point Hadamard rotation, whole-row kernel, column-absmax kernel.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
@@ -20,12 +21,12 @@ int fail(int code, const char* fmt, ...) {
 int check_arch() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return fail(I8L_ERR_CUDA, "cudaGetDevice failed");
-  static int cached_major[64];  // 0 = unknown
-  int major = (dev >= 0 && dev < 64) ? cached_major[dev] : 0;
+  static std::atomic<int> cached_major[64];  // 0 = unknown
+  int major = (dev >= 0 && dev < 64) ? cached_major[dev].load(std::memory_order_relaxed) : 0;
   if (major == 0) {
     if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
       return fail(I8L_ERR_CUDA, "cudaDeviceGetAttribute failed");
-    if (dev >= 0 && dev < 64) cached_major[dev] = major;
+    if (dev >= 0 && dev < 64) cached_major[dev].store(major, std::memory_order_relaxed);
   }
   if (major != 10)
     return fail(I8L_ERR_ARCH, "device %d has compute capability %d.x; this library is sm_100a only", dev, major);
@@ -214,6 +215,42 @@ quant_tile_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t col
       *reinterpret_cast<uint32_t*>(qtb + (c_base + c) * rows + r_base + 4 * l) = word;
     }
   }
+}
+
+// ------------------------------------------------------------------------------------------------
+// One scale per 128 rows x 256 columns (the activation grouping of the reference's TileLang forward).
+// One CTA of 256 threads per group: warp w holds rows 16w..16w+15, one 16-byte piece per lane and row
+// (32 lanes cover the 512-byte row segment), 64 registers of packed bf16 per thread.
+// ------------------------------------------------------------------------------------------------
+template <int MODE>
+__global__ void __launch_bounds__(256, 3)
+quant_tile256_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t cols, int8_t* __restrict__ q,
+                     float* __restrict__ scale) {
+  __shared__ float s_red[8];
+  const int tid = threadIdx.x, w = tid >> 5, l = tid & 31;
+  const int64_t r_base = (int64_t)blockIdx.y * 128, c_base = (int64_t)blockIdx.x * 256;
+  const int64_t boff = (int64_t)blockIdx.z * rows * cols;
+  uint4 raw[16];
+  __nv_bfloat162 m2 = __floats2bfloat162_rn(0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    raw[i] = __ldg(reinterpret_cast<const uint4*>(x + boff + (r_base + 16 * w + i) * cols + c_base + 8 * l));
+    m2 = absmax8(raw[i], m2);
+  }
+  float m = hmax_of(m2);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (l == 0) s_red[w] = m;
+  __syncthreads();
+  m = s_red[0];
+#pragma unroll
+  for (int k = 1; k < 8; ++k) m = fmaxf(m, s_red[k]);
+  float s, stored;
+  make_scale<MODE>(m, s, stored);
+  if (tid == 0) scale[((int64_t)blockIdx.z * (rows / 128) + blockIdx.y) * (cols / 256) + blockIdx.x] = stored;
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    *reinterpret_cast<uint2*>(q + boff + (r_base + 16 * w + i) * cols + c_base + 8 * l) = quant_piece<MODE>(raw[i], s);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -578,6 +615,23 @@ quant_row_hadfull_kernel(const __nv_bfloat16* __restrict__ x, int64_t cols, int8
 }
 
 // ------------------------------------------------------------------------------------------------ host
+constexpr int MAX_DEVICES = 64;
+static int device_ordinal() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return (dev < 0 || dev >= MAX_DEVICES) ? 0 : dev;
+}
+// Raises a kernel's dynamic shared-memory limit once per device (function attributes are per device;
+// the call is idempotent, so two threads racing here only repeat it).
+template <typename Kernel>
+static cudaError_t ensure_smem(Kernel kernel, std::atomic<bool>* done_per_device, size_t bytes) {
+  std::atomic<bool>& done = done_per_device[device_ordinal()];
+  if (done.load(std::memory_order_acquire)) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess) done.store(true, std::memory_order_release);
+  return e;
+}
+
 static int check_dims(int64_t batch, int64_t rows, int64_t cols) {
   if (batch <= 0 || rows <= 0 || cols <= 0 || rows % 128 || cols % 128)
     return fail(I8L_ERR_SHAPE, "batch=%lld rows=%lld cols=%lld: all must be positive and rows, cols multiples of 128",
@@ -606,11 +660,8 @@ static int dispatch_tile(const void* x, int64_t batch, int64_t rows, int64_t col
     }
     if (t) {
       constexpr size_t smem = 128 * 132 * sizeof(float);
-      static bool attr_done = false;
-      if (!attr_done) {
-        I8L_CUDA_OK(cudaFuncSetAttribute(quant_tile_hadrows_kernel<GRAN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_done = true;
-      }
+      static std::atomic<bool> attr_done[MAX_DEVICES];
+      I8L_CUDA_OK(ensure_smem(quant_tile_hadrows_kernel<GRAN, MODE>, attr_done, smem));
       dim3 grid((unsigned)(cols / 128), (unsigned)(rows / 128), (unsigned)batch);
       quant_tile_hadrows_kernel<GRAN, MODE><<<grid, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(x), rows, cols, qt, scale_t, nullptr);
     }
@@ -643,6 +694,16 @@ extern "C" int i8l_quant_tile(const void* x, int64_t batch, int64_t rows, int64_
   if (int e = check_arch()) return e;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool had = hadamard == I8L_HAD_128;
+  if (gran == I8L_GRAN_TILE128X256) {
+    if (cols % 256 || had || qt || !q) return fail(I8L_ERR_ARG, "i8l_quant_tile: 128x256 groups need cols %% 256 == 0, no rotation, q only");
+    const dim3 grid((unsigned)(cols / 256), (unsigned)(rows / 128), (unsigned)batch);
+    const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+    if (qmode == I8L_QMODE_TRITON) quant_tile256_kernel<I8L_QMODE_TRITON><<<grid, 256, 0, st>>>(xp, rows, cols, q, scale);
+    else if (qmode == I8L_QMODE_TRITON_BF16S) quant_tile256_kernel<I8L_QMODE_TRITON_BF16S><<<grid, 256, 0, st>>>(xp, rows, cols, q, scale);
+    else return fail(I8L_ERR_ARG, "i8l_quant_tile: 128x256 groups support qmode TRITON and TRITON_BF16S");
+    I8L_CUDA_OK(cudaGetLastError());
+    return I8L_OK;
+  }
 #define I8L_TILE_CASE(G, Mo) \
   if (gran == G && qmode == Mo) return dispatch_tile<G, Mo>(x, batch, rows, cols, had, q, scale, qt, scale_t, nullptr, st);
   I8L_TILE_CASE(I8L_GRAN_TILE128, I8L_QMODE_TRITON)
@@ -694,6 +755,7 @@ extern "C" int i8l_quant_row(const void* x, int64_t rows, int64_t cols, int qmod
   I8L_ROW_CASE(I8L_QMODE_TRITON)
   I8L_ROW_CASE(I8L_QMODE_RNE)
   I8L_ROW_CASE(I8L_QMODE_ROWRCP)
+  I8L_ROW_CASE(I8L_QMODE_TRITON_BF16S)
 #undef I8L_ROW_CASE
   return fail(I8L_ERR_ARG, "i8l_quant_row: unsupported qmode=%d", qmode);
 }
@@ -727,14 +789,9 @@ template <int MODE>
 static int launch_col_t_rot(const void* x, int64_t rows, int64_t cols, int8_t* qt, float* scale_t, float* colmax,
                             cudaStream_t st) {
   constexpr size_t smem = 128 * 132 * sizeof(float);
-  static bool attr_done = false;
-  if (!attr_done) {
-    I8L_CUDA_OK(cudaFuncSetAttribute(quant_tile_hadrows_kernel<GRAN_COLMAX_PASS, MODE>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    I8L_CUDA_OK(cudaFuncSetAttribute(quant_tile_hadrows_kernel<GRAN_COLFULL, MODE>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_done = true;
-  }
+  static std::atomic<bool> attr_done_pass[MAX_DEVICES], attr_done_full[MAX_DEVICES];
+  I8L_CUDA_OK(ensure_smem(quant_tile_hadrows_kernel<GRAN_COLMAX_PASS, MODE>, attr_done_pass, smem));
+  I8L_CUDA_OK(ensure_smem(quant_tile_hadrows_kernel<GRAN_COLFULL, MODE>, attr_done_full, smem));
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
   dim3 grid((unsigned)(cols / 128), (unsigned)(rows / 128), 1);
   quant_tile_hadrows_kernel<GRAN_COLMAX_PASS, MODE><<<grid, 256, smem, st>>>(xp, rows, cols, nullptr, nullptr, colmax);
@@ -763,20 +820,25 @@ extern "C" int i8l_quant_col_t_rot(const void* x, int64_t rows, int64_t cols, in
 // that device current) and cached.
 // ------------------------------------------------------------------------------------------------
 static __device__ __align__(256) float g_colmax_static[I8L_STATIC_SCRATCH_MAX_COLS];
-static float* g_colmax_static_addr[64];  // per device ordinal, nullptr = not looked up yet
+static std::atomic<float*> g_colmax_static_addr[MAX_DEVICES];  // per device ordinal, nullptr = not looked up yet
 
 extern "C" int i8l_quant_col_t_static(const void* x, int64_t rows, int64_t cols, int qmode, int8_t* qt,
                                       float* scale_t, void* stream) {
   if (cols > I8L_STATIC_SCRATCH_MAX_COLS)
     return fail(I8L_ERR_SHAPE, "i8l_quant_col_t_static: cols=%lld exceeds the built-in scratch of %d columns; "
                 "use i8l_quant_col_t with caller-provided scratch", (long long)cols, I8L_STATIC_SCRATCH_MAX_COLS);
+  // the same argument and device checks as i8l_quant_col_t, before the symbol query
+  if (int e = check_dims(1, rows, cols)) return e;
+  if (!x || !qt || !scale_t) return fail(I8L_ERR_ARG, "null pointer");
+  if (!aligned16(x) || !aligned16(qt)) return fail(I8L_ERR_ALIGN, "x, qt must be 16-byte aligned");
+  if (int e = check_arch()) return e;
   int dev = 0;
   I8L_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return fail(I8L_ERR_ARG, "device ordinal %d out of range", dev);
-  if (!g_colmax_static_addr[dev]) {
-    float* ptr = nullptr;
+  if (dev < 0 || dev >= MAX_DEVICES) return fail(I8L_ERR_ARG, "device ordinal %d out of range", dev);
+  float* ptr = g_colmax_static_addr[dev].load(std::memory_order_acquire);
+  if (!ptr) {
     I8L_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_colmax_static));
-    g_colmax_static_addr[dev] = ptr;
+    g_colmax_static_addr[dev].store(ptr, std::memory_order_release);
   }
-  return i8l_quant_col_t(x, rows, cols, qmode, qt, scale_t, g_colmax_static_addr[dev], stream);
+  return i8l_quant_col_t(x, rows, cols, qmode, qt, scale_t, ptr, stream);
 }

@@ -7,12 +7,79 @@ import torch
 from . import _lib as L
 
 
-def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
-
-
 def _ptr(t):
     return None if t is None else t.data_ptr()
+
+
+def _call(name: str, dev: torch.device, *args, tensors=()) -> None:
+    """Launch on `dev`: the C side takes the device, its SM count and the stream from the current CUDA
+    context, so the tensors' device is made current for the call (the trailing stream argument is that
+    device's current stream), and every operand must live on it."""
+    for t in tensors:
+        if t is not None and t.device != dev:
+            raise ValueError(f"{name}: operands on different devices ({t.device} vs {dev})")
+    with torch.cuda.device(dev):
+        L.call(name, *args, torch.cuda.current_stream(dev).cuda_stream)
+
+
+# ---------------------------------------------------------------------------------------- status word
+# The GEMM kernels bound every device-side wait; a wait that gives up makes the kernel return early and
+# write I8L_ERR_TIMEOUT into a device int32.  One such word per device is passed to every GEMM launched
+# from here.  check_status() reads it (synchronously); poll_status() is the cheap form for a training
+# loop: it looks at a copy started by the previous poll and starts the next one, never blocking.
+_STATUS: dict = {}
+
+
+class _StatusWord:
+    def __init__(self, dev):
+        self.dev = dev
+        self.word = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event = None
+
+
+def _status_of(dev: torch.device) -> "_StatusWord":
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    st = _STATUS.get(key)
+    if st is None:
+        st = _STATUS[key] = _StatusWord(torch.device("cuda", key))
+    return st
+
+
+def device_status(dev) -> torch.Tensor:
+    """The int32 status word that GEMMs on `dev` report into (0 = no wait has ever given up)."""
+    return _status_of(torch.device(dev)).word
+
+
+def _raise_if_set(st: "_StatusWord", code: int) -> None:
+    if code:
+        st.word.zero_()
+        st.host.zero_()
+        raise L.I8LError(code, f"a GEMM on {st.dev} gave up a bounded device-side wait; its output is incomplete")
+
+
+def check_status(dev=None) -> None:
+    """Synchronous check: raises I8LError (code TIMEOUT) if a GEMM on `dev` gave up a wait since the
+    last check, and clears the word."""
+    st = _status_of(torch.device(dev if dev is not None else ("cuda", torch.cuda.current_device())))
+    st.event = None
+    _raise_if_set(st, int(st.word.item()))
+
+
+def poll_status(dev) -> None:
+    """Non-blocking check for hot loops: raises if the copy started by an earlier poll has completed and
+    shows a timeout; then starts the next copy.  Does nothing while the stream is being captured."""
+    st = _status_of(torch.device(dev))
+    if torch.cuda.is_current_stream_capturing():
+        return
+    if st.event is not None:
+        if not st.event.query():
+            return
+        st.event = None
+        _raise_if_set(st, int(st.host[0]))
+    st.host.copy_(st.word, non_blocking=True)
+    st.event = torch.cuda.Event()
+    st.event.record(torch.cuda.current_stream(st.dev))
 
 
 def _check_bf16(x: torch.Tensor, name: str) -> torch.Tensor:
@@ -31,14 +98,13 @@ def quant_tile(x: torch.Tensor, gran: int = L.GRAN_TILE128, qmode: int = L.QMODE
     q = s = qt = st = None
     if natural:
         q = torch.empty((B, R, C), dtype=torch.int8, device=x.device)
-        s = torch.empty((B, R // 128, C // 128) if gran == L.GRAN_TILE128 else (B, R, C // 128),
-                        dtype=torch.float32, device=x.device)
+        s_shape = {L.GRAN_TILE128: (B, R // 128, C // 128), L.GRAN_TILE128X256: (B, R // 128, C // 256)}.get(gran, (B, R, C // 128))
+        s = torch.empty(s_shape, dtype=torch.float32, device=x.device)
     if transposed:
         qt = torch.empty((B, C, R), dtype=torch.int8, device=x.device)
         st = torch.empty((B, C // 128, R // 128) if gran == L.GRAN_TILE128 else (B, C, R // 128),
                          dtype=torch.float32, device=x.device)
-    L.call("i8l_quant_tile", x.data_ptr(), B, R, C, gran, qmode, hadamard, _ptr(q), _ptr(s), _ptr(qt), _ptr(st),
-           _stream())
+    _call("i8l_quant_tile", x.device, x.data_ptr(), B, R, C, gran, qmode, hadamard, _ptr(q), _ptr(s), _ptr(qt), _ptr(st))
     return q, s, qt, st
 
 
@@ -49,7 +115,7 @@ def quant_row(x: torch.Tensor, qmode: int = L.QMODE_TRITON, hadamard: int = 0):
     rows = x.numel() // C
     q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
     s = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
-    L.call("i8l_quant_row", x.data_ptr(), rows, C, qmode, hadamard, q.data_ptr(), s.data_ptr(), _stream())
+    _call("i8l_quant_row", x.device, x.data_ptr(), rows, C, qmode, hadamard, q.data_ptr(), s.data_ptr())
     return q, s
 
 
@@ -63,8 +129,8 @@ def quant_col_t(x: torch.Tensor, qmode: int = L.QMODE_TRITON, hadamard: int = 0)
     scratch = torch.empty((C,), dtype=torch.float32, device=x.device)
     if hadamard not in (0, 128):
         raise ValueError("quant_col_t: hadamard must be 0 or 128")
-    L.call("i8l_quant_col_t_rot" if hadamard else "i8l_quant_col_t", x.data_ptr(), R, C, qmode, qt.data_ptr(),
-           st.data_ptr(), scratch.data_ptr(), _stream())
+    _call("i8l_quant_col_t_rot" if hadamard else "i8l_quant_col_t", x.device, x.data_ptr(), R, C, qmode, qt.data_ptr(),
+          st.data_ptr(), scratch.data_ptr())
     return qt, st
 
 
@@ -85,9 +151,11 @@ def gemm_block(aq, bq, a_s, b_s, a_kind=L.ASCALE_TILE, b_kind=L.BSCALE_CHANNEL, 
     aq, bq = aq.contiguous(), bq.contiguous()
     B, M, N, K, bb = _gemm_dims(aq, bq)
     out = torch.empty((B, M, N), dtype=torch.float32 if flags & L.GEMM_OUT_F32 else torch.bfloat16, device=aq.device)
-    L.call("i8l_gemm_block", aq.data_ptr(), bq.data_ptr(), a_s.contiguous().data_ptr(), b_s.contiguous().data_ptr(),
-           a_kind, b_kind, int(bb), _ptr(bias), float(post_scale), out.data_ptr(), B, M, N, K, flags, _ptr(status),
-           _stream())
+    a_s, b_s = a_s.contiguous(), b_s.contiguous()
+    status = device_status(aq.device) if status is None else status
+    _call("i8l_gemm_block", aq.device, aq.data_ptr(), bq.data_ptr(), a_s.data_ptr(), b_s.data_ptr(),
+          a_kind, b_kind, int(bb), _ptr(bias), float(post_scale), out.data_ptr(), B, M, N, K, flags, _ptr(status),
+          tensors=(bq, a_s, b_s, bias, status))
     return out
 
 
@@ -95,8 +163,11 @@ def gemm_rowcol(aq, bq, a_s, b_s, bias=None, post_scale=1.0, flags=0, status=Non
     aq, bq = aq.contiguous(), bq.contiguous()
     B, M, N, K, bb = _gemm_dims(aq, bq)
     out = torch.empty((B, M, N), dtype=torch.float32 if flags & L.GEMM_OUT_F32 else torch.bfloat16, device=aq.device)
-    L.call("i8l_gemm_rowcol", aq.data_ptr(), bq.data_ptr(), a_s.contiguous().data_ptr(), b_s.contiguous().data_ptr(),
-           int(bb), _ptr(bias), float(post_scale), out.data_ptr(), B, M, N, K, flags, _ptr(status), _stream())
+    a_s, b_s = a_s.contiguous(), b_s.contiguous()
+    status = device_status(aq.device) if status is None else status
+    _call("i8l_gemm_rowcol", aq.device, aq.data_ptr(), bq.data_ptr(), a_s.data_ptr(), b_s.data_ptr(),
+          int(bb), _ptr(bias), float(post_scale), out.data_ptr(), B, M, N, K, flags, _ptr(status),
+          tensors=(bq, a_s, b_s, bias, status))
     return out
 
 
@@ -105,8 +176,9 @@ def gemm_dump_i32(aq, bq, per_block=False, status=None):
     B, M, N, K, bb = _gemm_dims(aq, bq)
     shape = (B, K // 128, M, N) if per_block else (B, M, N)
     out = torch.empty(shape, dtype=torch.int32, device=aq.device)
-    L.call("i8l_gemm_dump_i32", aq.data_ptr(), bq.data_ptr(), int(bb), out.data_ptr(), B, M, N, K, int(per_block),
-           _ptr(status), _stream())
+    status = device_status(aq.device) if status is None else status
+    _call("i8l_gemm_dump_i32", aq.device, aq.data_ptr(), bq.data_ptr(), int(bb), out.data_ptr(), B, M, N, K, int(per_block),
+          _ptr(status), tensors=(bq, status))
     return out
 
 
@@ -121,9 +193,11 @@ def gemm_block_scatter(aq, bq, a_s, b_s, slot_ptrs, rank: int, b_kind=L.BSCALE_C
         raise ValueError("gemm_block_scatter: one batch, shared B operand")
     world = len(slot_ptrs)
     arr = (ctypes.c_void_p * world)(*[int(p) for p in slot_ptrs])
-    L.call("i8l_gemm_block_scatter", aq.data_ptr(), bq.data_ptr(), a_s.contiguous().data_ptr(),
-           b_s.contiguous().data_ptr(), b_kind, float(post_scale), ctypes.cast(arr, ctypes.c_void_p), world, int(rank),
-           M, N, K, _ptr(status), _stream())
+    a_s, b_s = a_s.contiguous(), b_s.contiguous()
+    status = device_status(aq.device) if status is None else status
+    _call("i8l_gemm_block_scatter", aq.device, aq.data_ptr(), bq.data_ptr(), a_s.data_ptr(),
+          b_s.data_ptr(), b_kind, float(post_scale), ctypes.cast(arr, ctypes.c_void_p), world, int(rank),
+          M, N, K, _ptr(status), tensors=(bq, a_s, b_s, status))
 
 
 def sum_slots(slots: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -133,5 +207,5 @@ def sum_slots(slots: torch.Tensor, out: torch.Tensor | None = None) -> torch.Ten
     world, rows, cols = slots.shape
     if out is None:
         out = torch.empty((rows, cols), dtype=torch.bfloat16, device=slots.device)
-    L.call("i8l_sum_slots", slots.data_ptr(), out.data_ptr(), world, rows, cols, _stream())
+    _call("i8l_sum_slots", slots.device, slots.data_ptr(), out.data_ptr(), world, rows, cols, tensors=(out,))
     return out

@@ -158,6 +158,9 @@ class Int8LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, cfg: Int8Config):
         x2 = x.reshape(-1, x.shape[-1])
+        # Every GEMM reports a device-side wait that gave up into the device's status word; look at it
+        # here without blocking (the copy was started by the previous call) and raise if it is set.
+        K.poll_status(x.device)
         need_w = weight.requires_grad
         y, saved_xt = linear_forward(x2, weight, bias, cfg, want_xt=need_w)
         ctx.cfg = cfg
