@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the INT8 quantized-linear hot path (forward + dX + dW of one linear layer).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c5|c3|c2|c1|sq8192|c2sq8192|c5dc]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c5|c4|c3|c2|c1|sq8192|c2sq8192|c5dc]
 
 Workload (default c5): the Llama-70B MLP shape M=32768 tokens, K=8192, N=28672, block_channel
 scaling, W column-sharded along N over the N GPUs (strong scaling); synthetic seeded data with the
@@ -42,6 +42,7 @@ WORKLOADS = {
     "c1": (512, 1024, 1024, "config-1 512x1024x1024 block_channel fwd+dX+dW"),
     "c2": (8192, 4096, 4096, "config-2 double_channel forward M=8192 K=4096 N=4096 (full Hadamard, bias)"),
     "c2sq8192": (8192, 8192, 8192, "double_channel forward 8192^3 (full Hadamard)"),
+    "c4": (8192, 4096, 11008, "llama2-7b decoder layer at M=8192 tokens (batch 4 x seq 2048): seven block_channel INT8 linears (q/k/v/o 4096->4096, gate/up 4096->11008, down 11008->4096) chained through norm, causal attention, SiLU gate and residuals; forward + backward"),
     "c5dc": (32768, 8192, 28672, "llama70b-mlp M=32768 K=8192 N=28672 double_channel fwd+dX+dW (per-row scales, whole-K int32 accumulation, no rotation)"),
 }
 NOMINAL_INT8_TOPS = 4500.0  # B200 dense INT8 datasheet figure
@@ -235,6 +236,8 @@ def main():
     ap.add_argument("--reduce-scatter", default="nccl", choices=["peer", "nccl"],
                     help="N>1: dX partials scattered by the GEMM epilogue into peer memory (default; falls back to\n"
                          "nccl when the peer mapping cannot be set up), or a separate NCCL reduce-scatter")
+    ap.add_argument("--comm-sms", type=int, default=16,
+                    help="N>1: SMs the dW GEMM leaves to the NCCL reduce-scatter that runs beside it (0 = none)")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time the step launch by launch even on one GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -268,7 +271,7 @@ def main():
     lo, hi = tp.shard_bounds(N, world, rank)
     Nl = hi - lo
     x, w, dy = make_inputs(M, K, Nl, rank, dev)
-    step_obj = tp.ColumnParallelStep(None if world == 1 else dist.group.WORLD, DEFAULT)
+    step_obj = tp.ColumnParallelStep(None if world == 1 else dist.group.WORLD, DEFAULT, comm_sms=args.comm_sms)
     peer_slots, rs_mode = None, "none"
     if world > 1:
         rs_mode = "nccl reduce_scatter_tensor on a side stream, overlapped with the dW GEMM"
@@ -292,6 +295,47 @@ def main():
 
     ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
     gemm_events = []
+
+    if args.workload == "c4":
+        # The chained decoder layer: the seven linears are the library's; norm, attention, gate and residual
+        # adds are ordinary PyTorch and are timed with them (the step is what a training loop would run).
+        if world > 1:
+            raise SystemExit("the decoder-layer workload is single-GPU")
+        from triton_int8_b200.decoder_layer import DecoderLayer
+        torch.manual_seed(4)
+        layer = DecoderLayer(K, 32, N, device=dev)
+        twin = DecoderLayer(K, 32, N, device=dev, linear_cls=torch.nn.Linear)
+        twin.load_state_dict(layer.state_dict())
+        xin = torch.randn(4, M // 4, K, device=dev).to(torch.bfloat16)
+        dout = (torch.randn(4, M // 4, K, device=dev) * 1e-3).to(torch.bfloat16)
+
+        def run(mod):
+            xi = xin.clone().requires_grad_(True)
+            mod(xi).backward(dout)
+            for p_ in mod.parameters():
+                p_.grad = None
+
+        def time_mod(mod):
+            for _ in range(max(args.warmup, 3)):
+                run(mod)
+            torch.cuda.synchronize()
+            t0, t1 = ev(), ev()
+            t0.record()
+            for _ in range(args.steps):
+                run(mod)
+            t1.record(); torch.cuda.synchronize()
+            return t0.elapsed_time(t1) / args.steps
+        ms, ms_bf16 = time_mod(layer), time_mod(twin)
+        Kn.check_status(dev)
+        lin_ops = 6.0 * M * (4 * K * K + 3 * K * N)
+        print(json.dumps({
+            "metric": "decoder_layer_fwd_bwd_tokens_per_s", "value": M / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": desc, "M": M, "hidden": K, "mlp": N, "heads": 32},
+            "bf16_twin_ms_per_step": ms_bf16, "speedup_vs_bf16_twin": ms_bf16 / ms,
+            "linear_tops_if_all_time_were_linears": lin_ops / ms / 1e9, "gpu_launches": 7 * 8 * args.steps}))
+        return
 
     if args.workload == "c5dc":
         # The same linear layer with the double_channel scaling: three whole-K GEMMs (no per-128-K promotion).
@@ -357,14 +401,12 @@ def main():
 
     from triton_int8_b200.linear import Int8Config
     cfg = Int8Config(hadamard=had)
-    launches_per_step = 10 if had else 8
+    launches_per_step = 8   # X, W, dY quantizers (one kernel each), W^T (column absmax + quantize), three GEMMs
 
     def step(record=False):
         # forward
         _, saved_xt_unused = None, None
-        xq, xs, xqt, xst = Kn.quant_tile(x[None], cfg.gran, cfg.qmode, had, natural=True, transposed=not had)
-        if had:   # the dW operand X^T is rotated along the tokens: its own pass
-            _, _, xqt, xst = Kn.quant_tile(x[None], cfg.gran, cfg.qmode, had, natural=False, transposed=True)
+        xq, xs, xqt, xst = Kn.quant_tile(x[None], cfg.gran, cfg.qmode, had, natural=True, transposed=True)   # X and X^T from one read
         wq, ws = Kn.quant_row(w, cfg.qmode, had)
         e = [ev() for _ in range(6)] if record else None
         if record: e[0].record()
@@ -391,7 +433,8 @@ def main():
         else:
             dx = dx_partial
         if record: e[4].record()
-        dw = grad_weight(dyt_op, (xqt, xst), cfg)
+        with Kn.cta_limit(step_obj.dw_ctas if (world > 1 and peer_slots is None) else 0):
+            dw = grad_weight(dyt_op, (xqt, xst), cfg)   # beside the reduce-scatter: leaves SMs to the collective
         if record: e[5].record()
         if world > 1 and peer_slots is None:
             torch.cuda.current_stream().wait_stream(step_obj.comm_stream)
@@ -485,6 +528,18 @@ def main():
     if world > 1:
         dist.all_reduce(worst, op=dist.ReduceOp.MAX)
     parity["worst_calc_diff_over_gate_over_ranks"] = worst.item()
+    if world > 1:   # the all-gathered int8 operands of the row-sharded X equal the locally quantized whole X
+        mlo_, mhi_ = tp.shard_bounds(M, world, rank)
+        (gq, gs), (gqt, gst) = tp.gather_quantized_activations(x[mlo_:mhi_].contiguous(), cfg)
+        lq, ls, _, _ = Kn.quant_tile(x[None], cfg.gran, cfg.qmode, had, natural=True, transposed=False)
+        _, _, lqt, lst = Kn.quant_tile(x[None], cfg.gran, cfg.qmode, had, natural=False, transposed=True)
+        same = all(torch.equal(a_, b_) for a_, b_ in ((gq, lq), (gs, ls), (gqt, lqt), (gst, lst)))
+        flag = torch.tensor([1.0 if same else 0.0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        parity["sharded_x_operands_bit_identical"] = bool(flag.item() == 1.0)
+        if not parity["sharded_x_operands_bit_identical"]:
+            worst += 10.0
+        del gq, gs, gqt, gst, lq, ls, lqt, lst
     parity["gate"] = {"what": "calc_diff vs the fp32 product of the same bf16 operands, on every rank", **gates}
     parity["ok"] = bool(worst.item() < 1.0)
     del out, y, dx, dw, y_ref, dx_ref, dw_ref, par
@@ -605,28 +660,44 @@ def main():
     e2e = None
     if not args.no_e2e:
         from triton_int8_b200.linear import Int8Linear
-        xh = x.cpu().pin_memory()
-        dyh = dy.cpu().pin_memory()
-        lin = Int8Linear(K, Nl, bias=False, device=dev, config=cfg)
-        with torch.no_grad():
-            lin.weight.copy_(w)
-        res_h = torch.empty(3, dtype=torch.float32).pin_memory()
-
         from triton_int8_b200.hostio import HostPrefetcher
-        feed = HostPrefetcher(lambda: (xh, dyh), dev)   # every step copies X and dY from pinned host memory
+        dyh = dy.cpu().pin_memory()
+        res_h = torch.empty(3, dtype=torch.float32).pin_memory()
+        if world == 1:
+            xh = x.cpu().pin_memory()
+            lin = Int8Linear(K, Nl, bias=False, device=dev, config=cfg)
+            with torch.no_grad():
+                lin.weight.copy_(w)
+            feed = HostPrefetcher(lambda: (xh, dyh), dev)   # every step copies X and dY from pinned host memory
+            e2e_api = "Int8Linear.forward + autograd backward; X and dY copied from pinned host memory every step"
 
-        def e2e_step():
-            xd, dyd = feed.get()                         # copy of the next step overlaps this step's compute
-            xd = xd.detach().requires_grad_(True)
-            yy = lin(xd)
-            yy.backward(dyd)
-            dxp = xd.grad
-            if world > 1:
-                dxp = tp.reduce_scatter_rows(dxp)
-            r = torch.stack([yy[0, :128].float().sum(), dxp[0, :128].float().sum(), lin.weight.grad[0, :128].float().sum()])
-            res_h.copy_(r, non_blocking=True)
-            feed.done()
-            lin.weight.grad = None
+            def e2e_step():
+                xd, dyd = feed.get()                         # copy of the next step overlaps this step's compute
+                xd = xd.detach().requires_grad_(True)
+                yy = lin(xd)
+                yy.backward(dyd)
+                r = torch.stack([yy[0, :128].float().sum(), xd.grad[0, :128].float().sum(), lin.weight.grad[0, :128].float().sum()])
+                res_h.copy_(r, non_blocking=True)
+                feed.done()
+                lin.weight.grad = None
+        else:
+            # Column-parallel: X is one replicated activation, so each rank copies only ITS M/g rows from the
+            # host, quantizes them and all-gathers the int8 operands over NVLink (tp.gather_quantized_activations);
+            # its dY column shard comes from the host in full.
+            mlo, mhi = tp.shard_bounds(M, world, rank)
+            xh = x[mlo:mhi].cpu().pin_memory()
+            e2e_obj = tp.ColumnParallelStep(dist.group.WORLD, cfg, comm_sms=args.comm_sms)
+            feed = HostPrefetcher(lambda: (xh, dyh), dev)
+            e2e_api = ("tp.ColumnParallelStep.forward_sharded + backward; every rank copies its M/g rows of X and its dY shard "
+                       "from pinned host memory every step, int8 X operands all-gathered over NVLink")
+
+            def e2e_step():
+                xd, dyd = feed.get()
+                yy, saved = e2e_obj.forward_sharded(xd, w)
+                dxp, dwp = e2e_obj.backward(dyd, w, saved)
+                r = torch.stack([yy[0, :128].float().sum(), dxp[0, :128].float().sum(), dwp[0, :128].float().sum()])
+                res_h.copy_(r, non_blocking=True)
+                feed.done()
         n_e2e = max(2, min(args.steps, 5))
         e2e_step(); sync_all()
         ems = None
@@ -642,10 +713,12 @@ def main():
                 dist.all_reduce(tms, op=dist.ReduceOp.MAX)
                 t_pass = tms.item()
             ems = t_pass if ems is None else min(ems, t_pass)
+        per_rank = xh.numel() * 2 + dyh.numel() * 2
         e2e = {"value": M / (ems / n_e2e * 1e-3), "unit": "tokens/s",
-               "h2d_bytes_per_step": xh.numel() * 2 + dyh.numel() * 2, "d2h_bytes_per_step": 12,
-               "api": "Int8Linear.forward + autograd backward; X and dY copied from pinned host memory every step, copy of step i+1 overlapped with step i (HostPrefetcher); best of 3 passes"}
-        del xh, dyh, lin
+               "h2d_bytes_per_step": per_rank * world, "d2h_bytes_per_step": 12 * world,
+               "h2d_bytes_per_step_per_rank": per_rank,
+               "api": e2e_api + "; copy of step i+1 overlapped with step i (HostPrefetcher); best of 3 passes"}
+        del xh, dyh
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

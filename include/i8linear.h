@@ -212,6 +212,16 @@ I8L_API int i8l_gemm_block_scatter(const int8_t* a_q, const int8_t* b_q, const f
 I8L_API int i8l_sum_slots(const void* slots, void* out, int world, int64_t rows, int64_t cols, void* stream);
 
 /*
+ * The GEMMs are persistent kernels with one CTA per SM (about 210 KB of shared memory each), so a kernel
+ * launched beside one on another stream finds no free SM until the GEMM ends.  This sets, for the calling
+ * host thread, the number of CTAs the following GEMM launches may use (0 = all SMs, the default): a
+ * column-parallel backward pass gives the dW GEMM a few SMs fewer while the reduce-scatter of dX is in
+ * flight, so that the collective overlaps the GEMM instead of queueing behind it.  No counterpart in the
+ * reference (it has no multi-GPU code).
+ */
+I8L_API int i8l_set_cta_limit(int max_ctas);
+
+/*
  * Test hook for the bounded waits of the GEMM kernels (not for production use; process-wide until reset).
  * Every wait on an mbarrier inside the GEMMs gives up after a number of polls (about two seconds' worth)
  * and the kernel then returns with I8L_ERR_TIMEOUT in the caller's status word instead of hanging.

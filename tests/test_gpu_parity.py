@@ -320,3 +320,60 @@ def test_rowcol_fp32_output_applies_post_scale_and_bias():
         ref = R.gemm_rowcol(aq, wq, a_s, w_s) * post + bias.float()
         got = DC.int8_gemm_pipeline(a.to(DEV), w.to(DEV), out_dtype=torch.float32, hadamard=had, bias=bias.to(DEV))
         _same(got, ref, f"fp32 double_channel pipeline, hadamard={had}")
+
+
+@pytest.mark.parametrize("mode", ["triton", "rne"])
+def test_rotated_operand_pair_from_one_read(mode):
+    """hadamard=128 with both outputs requested: q (rotated along the columns) and qt (the transpose,
+    rotated along the rows) come from one kernel that reads each tile once; both must equal the oracle,
+    and the two single-output kernels, bit for bit."""
+    g = torch.Generator().manual_seed(23)
+    x = (torch.randn(2, 384, 256, generator=g) * 2).to(torch.bfloat16)
+    x[0, :128, :128] = 0
+    x[1, 130, 7] = -90.0
+    x[0, 200:210, 129] = 33.0
+    Mo = L.QMODE_TRITON if mode == "triton" else L.QMODE_RNE
+    oracle = R.quant_tile128 if mode == "triton" else R.quant_tile128_rne
+    q, s, qt, st = K.quant_tile(x.to(DEV), L.GRAN_TILE128, Mo, 128, natural=True, transposed=True)
+    q_ref, s_ref = oracle(R.hadamard(x, 128))
+    qt_ref, st_ref = oracle(R.hadamard(x.transpose(1, 2).contiguous(), 128))
+    _same(q, q_ref, "q"); _same(s, s_ref, "scale"); _same(qt, qt_ref, "qt"); _same(st, st_ref, "scale_t")
+    q1, s1, _, _ = K.quant_tile(x.to(DEV), L.GRAN_TILE128, Mo, 128, natural=True, transposed=False)
+    _, _, qt1, st1 = K.quant_tile(x.to(DEV), L.GRAN_TILE128, Mo, 128, natural=False, transposed=True)
+    assert torch.equal(q, q1) and torch.equal(s, s1) and torch.equal(qt, qt1) and torch.equal(st, st1)
+
+
+@pytest.mark.parametrize("spread", ["smooth", "wild"])
+def test_fast_block_epilogue_accuracy_deep_k(spread):
+    """The fast block-scaled epilogue turns the int32 partials into floats by an integer add of a magic
+    number and lets the accumulators carry a bounded multiple of that number, removed at the tile end.
+    At K = 32768 (256 K blocks), with per-tile scales that are smooth or jump by three decades from one
+    K block to the next, the fp32 result must stay within 1e-4 (relative Frobenius) of the float64 value of
+    sum_kb P_kb * a_s * b_s, like the reference-order mode."""
+    M, N, Kd = 256, 512, 32768
+    g = torch.Generator().manual_seed(41)
+    aq, bq = _randq(g, 1, M, Kd), _randq(g, N, Kd)
+    if spread == "smooth":
+        a_s = torch.rand(1, M // 128, Kd // 128, generator=g) * 0.5 + 0.75
+    else:
+        a_s = 10.0 ** (torch.rand(1, M // 128, Kd // 128, generator=g) * 3.0 - 1.5)
+    b_s = torch.rand(N, generator=g) + 0.5
+    ref = torch.zeros(M, N, dtype=torch.float64)
+    for kb in range(Kd // 128):
+        P = R.int_mm(aq[0, :, kb * 128:(kb + 1) * 128], bq[:, kb * 128:(kb + 1) * 128]).double()
+        ref += P * a_s[0, :, kb].double().repeat_interleave(128).view(M, 1)
+    ref *= b_s.double().view(1, N)
+    args = (aq.to(DEV), bq.to(DEV), a_s.to(DEV), b_s.to(DEV))
+    fast = K.gemm_block(*args, flags=L.GEMM_OUT_F32)[0].cpu().double()
+    exact = K.gemm_block(*args, flags=L.GEMM_OUT_F32 | L.GEMM_EXACT_ORDER)[0].cpu().double()
+    e_fast, e_exact = R.rel_fro(fast, ref), R.rel_fro(exact, ref)
+    assert e_exact < 1e-6, e_exact
+    assert e_fast < 1e-4, (e_fast, e_exact)
+    # tile x tile scales (the dW layout) through the same kind
+    b_t = torch.rand(N // 128, Kd // 128, generator=g) + 0.5
+    ref2 = torch.zeros(M, N, dtype=torch.float64)
+    for kb in range(Kd // 128):
+        P = R.int_mm(aq[0, :, kb * 128:(kb + 1) * 128], bq[:, kb * 128:(kb + 1) * 128]).double()
+        ref2 += P * a_s[0, :, kb].double().repeat_interleave(128).view(M, 1) * b_t[:, kb].double().repeat_interleave(128).view(1, N)
+    fast2 = K.gemm_block(args[0], args[1], args[2], b_t.to(DEV), b_kind=L.BSCALE_TILE, flags=L.GEMM_OUT_F32)[0].cpu().double()
+    assert R.rel_fro(fast2, ref2) < 1e-4

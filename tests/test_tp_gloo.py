@@ -42,6 +42,18 @@ def _worker(rank, world, port, scenario, q):
             exact = dy.float() @ w.float()
             err = R.rel_fro(dx_r, exact[mlo:mhi])
             q.put((rank, ok, err))
+        elif scenario == "gather":
+            # each rank quantizes only its rows of X (both orientations); the gathered operands must equal
+            # what the whole X gives, bit for bit (tile scales are local to 128-row blocks)
+            mlo, mhi = tp.shard_bounds(M, world, rank)
+            x_l = x[mlo:mhi]
+            q_l, s_l = R.quant_tile128(x_l[None])
+            qt_l, st_l = R.quant_tile128(x_l.t().contiguous()[None])
+            (xq, xs), (xqt, xst) = tp.gather_row_sharded_operands(q_l, s_l, qt_l, st_l)
+            q_f, s_f = R.quant_tile128(x[None])
+            qt_f, st_f = R.quant_tile128(x.t().contiguous()[None])
+            ok = all(torch.equal(a_, b_) for a_, b_ in ((xq, q_f), (xs, s_f), (xqt, qt_f), (xst, st_f)))
+            q.put((rank, ok, 0.0))
         elif scenario == "mismatch":
             tp.set_shape_checks(True)
             part = torch.zeros(M if rank == 0 else M // 2, K)
@@ -54,7 +66,7 @@ def _worker(rank, world, port, scenario, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("scenario", ["algebra", "mismatch"])
+@pytest.mark.parametrize("scenario", ["algebra", "gather", "mismatch"])
 def test_two_rank_column_parallel(scenario):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()

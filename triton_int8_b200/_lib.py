@@ -35,6 +35,7 @@ SIGNATURES = {
     "i8l_gemm_dump_i32": [_P, _P, _I, _P, _I64, _I64, _I64, _I64, _I, _P, _P],
     "i8l_gemm_block_scatter": [_P, _P, _P, _P, _I, _F, _P, _I, _I, _I64, _I64, _I64, _P, _P],
     "i8l_sum_slots": [_P, _P, _I, _I64, _I64, _P],
+    "i8l_set_cta_limit": [_I],
     "i8l_test_set_wait_limit": [ctypes.c_uint32, _I],
     "i8l_version": [],
 }

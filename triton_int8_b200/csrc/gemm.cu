@@ -264,7 +264,8 @@ struct __align__(8) SharedCtl {
   int abort_flag;
   float bscale[EPI_WARPS / 4][EPI_COLS];     // per-tile column scales of each epilogue group (CHANNEL)
   float bstep[EPI_WARPS / 4][2][EPI_COLS];   // per-K-block column scales (GROUP), double buffered
-  float fac[EPI_WARPS / 4][FAC_MAX];         // per-K-block scalar factors of the current tile (K_BLOCK_FAST)
+  float fac[EPI_WARPS / 4][FAC_MAX];         // per-K-block scalar factors of the current tile (K_BLOCK_FAST), signed
+  float fbias[EPI_WARPS / 4][2];             // running sum of the signed factors of the current tile (value, error term)
 };
 
 // Epilogue kinds.  Everything but K_ROWCOL drains the accumulator every 128-wide K block.
@@ -273,6 +274,27 @@ constexpr int K_BLOCK_GEN = 1;   // block-scaled, any scale layout, reference op
 constexpr int K_BLOCK_FAST = 2;  // block-scaled, one scalar factor per (tile, K block) and 64-column group
 constexpr int K_BLOCK_ROWFAC = 4;  // block-scaled, per-(row, K block) A scale x per-tile or per-channel B scale
 constexpr int K_BLOCK_COLFAC = 3;  // block-scaled, per-tile A scale x per-(column, K block) B scale (fused forward)
+constexpr uint32_t MAGIC_I = 0x4B400000u;   // the bits of 1.5 * 2^23
+constexpr float MAGIC_F = 12582912.f;       // 1.5 * 2^23
+
+// Sixteen int32 partial products (|P| < 2^22) -> fp32, exactly.  The conversion instruction runs at half
+// rate on one pipe; MAGIC_I + P read as a float is 1.5*2^23 + P, and subtracting 1.5*2^23 (a packed add on
+// the other pipe) gives the same float(P).  Alternating the two forms between chunks balances the pipes
+// (measured 6 % faster than either alone).
+__device__ __forceinline__ void to_float16(bool via_add, const uint32_t* r, float* v) {
+  if (via_add) {
+    const float2 nm = make_float2(-MAGIC_F, -MAGIC_F);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float2 t = __fadd2_rn(make_float2(__uint_as_float(MAGIC_I + r[2 * j]), __uint_as_float(MAGIC_I + r[2 * j + 1])), nm);
+      v[2 * j] = t.x;
+      v[2 * j + 1] = t.y;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = __int2float_rn((int)r[j]);
+  }
+}
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
@@ -549,6 +571,26 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int i = tix; i < dn; i += 128)
               ctl.fac[wg][i] = __ldg(as_ptr + ((k0 + i) >> p.a_kshift)) * ((!chan && active) ? __ldg(bs_ptr + i) * p.post_scale : 1.f);
             named_sync(1 + wg, 128);
+            // Signs for the biased conversion (see the K-block loop): block d contributes g_d * (MAGIC_F + s_d P_d)
+            // with g_d = s_d f_d, so the accumulators carry MAGIC_F * sum(g) on top of sum(f P).  Choosing s_d
+            // against the sign of the running sum keeps |sum(g)| <= max f whatever the scales are, which bounds the
+            // rounding error the bias can cause; the sum is taken out again after the last K block.
+            if (tix == 0) {
+              // the sum as an unevaluated pair (run, low): its error times MAGIC_F would otherwise show in the result
+              float run = k0 == 0 ? 0.f : ctl.fbias[wg][0], low = k0 == 0 ? 0.f : ctl.fbias[wg][1];
+              for (int i = 0; i < dn; ++i) {
+                float g = ctl.fac[wg][i];
+                g = run > 0.f ? -g : g;
+                const float sum = __fadd_rn(run, g);
+                const float bb = __fsub_rn(sum, run);   // two-sum: the rounding error of run + g, off the critical chain
+                low = __fadd_rn(low, __fadd_rn(__fsub_rn(run, __fsub_rn(sum, bb)), __fsub_rn(g, bb)));
+                run = sum;
+                ctl.fac[wg][i] = g;
+              }
+              ctl.fbias[wg][0] = run;
+              ctl.fbias[wg][1] = low;
+            }
+            named_sync(1 + wg, 128);
           }
           for (int d = 0; d < dn; ++d) {
             float f;
@@ -563,22 +605,36 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               mbar_arrive(tempty0 + 8 * ab);   // every thread arrives for itself: no warp sync, no branch
             };
             if (active) {
+              // int32 -> fp32 without the conversion unit: |P| <= 128*127*127 < 2^22, so the integer MAGIC_I + P
+              // (or MAGIC_I - P), read as a float, IS the number 1.5*2^23 + P (or - P): one full-rate integer
+              // add per element instead of a half-rate conversion.  The factor carries the sign, so the product
+              // is f*P plus a multiple of MAGIC_F that the staging code keeps small and the tile end removes.
               const uint32_t taddr = taddr0 + ab * BN;
               const float2 f2 = make_float2(f, f);
+              if (f >= 0.f) {
 #pragma unroll
-              for (int c = 0; c < EPI_COLS / CH; ++c) {  // 8-column chunks: 16-column ones spill here
-                uint32_t r[CH];
-                tc_ld8(taddr + c * CH, r);
-                tc_ld_wait();
-                if (c == EPI_COLS / CH - 1) release();
-                // one conversion and half a packed FMA per accumulator element; each pass is a run of
-                // independent instructions
-                float v[CH];
+                for (int c = 0; c < EPI_COLS / CH; ++c) {  // 8-column chunks: 16-column ones spill here
+                  uint32_t r[CH];
+                  tc_ld8(taddr + c * CH, r);
+                  tc_ld_wait();
+                  if (c == EPI_COLS / CH - 1) release();
 #pragma unroll
-                for (int j = 0; j < CH; ++j) v[j] = __int2float_rn((int)r[j]);
+                  for (int j = 0; j < CH / 2; ++j)
+                    acc[c * (CH / 2) + j] = __ffma2_rn(make_float2(__uint_as_float(MAGIC_I + r[2 * j]), __uint_as_float(MAGIC_I + r[2 * j + 1])),
+                                                       f2, acc[c * (CH / 2) + j]);
+                }
+              } else {
 #pragma unroll
-                for (int j = 0; j < CH / 2; ++j)
-                  acc[c * (CH / 2) + j] = __ffma2_rn(make_float2(v[2 * j], v[2 * j + 1]), f2, acc[c * (CH / 2) + j]);
+                for (int c = 0; c < EPI_COLS / CH; ++c) {
+                  uint32_t r[CH];
+                  tc_ld8(taddr + c * CH, r);
+                  tc_ld_wait();
+                  if (c == EPI_COLS / CH - 1) release();
+#pragma unroll
+                  for (int j = 0; j < CH / 2; ++j)
+                    acc[c * (CH / 2) + j] = __ffma2_rn(make_float2(__uint_as_float(MAGIC_I - r[2 * j]), __uint_as_float(MAGIC_I - r[2 * j + 1])),
+                                                       f2, acc[c * (CH / 2) + j]);
+                }
               }
             } else {
               release();
@@ -592,11 +648,15 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           int t2 = t;
           asm volatile("" : "+r"(t2));  // keeps the tile's coordinates out of the K-block loop's live registers
           const TileCoord tc = unit_tile(t2);
+          // take out MAGIC_F * sum(g): the leading part first (close to the accumulator, so the difference is
+          // nearly exact), then the small remainder
+          const float b_hi = __fmul_rn(-MAGIC_F, ctl.fbias[wg][0]);
+          const float b_lo = __fmaf_rn(-MAGIC_F, ctl.fbias[wg][0], -b_hi) + __fmul_rn(-MAGIC_F, ctl.fbias[wg][1]);
           float out[EPI_COLS];
 #pragma unroll
           for (int j = 0; j < EPI_COLS / 2; ++j) {
-            out[2 * j] = acc[j].x;
-            out[2 * j + 1] = acc[j].y;
+            out[2 * j] = __fadd_rn(__fadd_rn(acc[j].x, b_hi), b_lo);
+            out[2 * j + 1] = __fadd_rn(__fadd_rn(acc[j].y, b_hi), b_lo);
           }
           int64_t row = (int64_t)tc.m_blk * BM + tix;
           void* cbase = p.c;
@@ -648,8 +708,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               // one conversion and half a packed FMA per accumulator element; each pass is a run of
               // independent instructions
               float v[16];
-#pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] = __int2float_rn((int)r[j]);
+              to_float16((c & 1) != 0, r, v);   // c is an unrolled loop index: the choice folds at compile time
 #pragma unroll
               for (int j = 0; j < 8; ++j)
                 acc[c * 8 + j] = __ffma2_rn(make_float2(v[2 * j], v[2 * j + 1]), f2, acc[c * 8 + j]);
@@ -711,8 +770,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               // one conversion and half a packed FMA per accumulator element; each pass is a run of
               // independent instructions
               float v[16];
-#pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] = __int2float_rn((int)r[j]);
+              to_float16((c & 1) != 0, r, v);   // c is an unrolled loop index: the choice folds at compile time
 #pragma unroll
               for (int j = 0; j < 8; ++j)
                 acc[c * 8 + j] = __ffma2_rn(make_float2(v[2 * j], v[2 * j + 1]), COLFAC ? fcol[c * 8 + j] : f2, acc[c * 8 + j]);
@@ -934,6 +992,9 @@ static int sm_count() {
   return n;
 }
 
+// i8l_set_cta_limit: CTAs a persistent GEMM launched by this host thread may occupy (0 = every SM).
+static thread_local int g_cta_limit = 0;
+
 // Test hooks (i8l_test_set_wait_limit): 0 = production values.
 static std::atomic<uint32_t> g_test_max_polls{0};
 static std::atomic<int> g_test_withhold{0};
@@ -968,6 +1029,10 @@ static int launch_kind(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
       units = n > 0 ? n : 1;
     }
     max_units[dev].store(units, std::memory_order_release);
+  }
+  if (g_cta_limit > 0) {   // leave SMs free for a kernel that runs beside this one
+    const int lim = TWO ? g_cta_limit / 2 : g_cta_limit;
+    units = units < lim ? units : (lim > 0 ? lim : 1);
   }
   const int grid_units = (int)(tiles < units ? tiles : units);
   cfg.gridDim = dim3(TWO ? 2 * grid_units : grid_units, 1, 1);
@@ -1019,7 +1084,8 @@ static int launch_gemm(bool block, const int8_t* a_q, const int8_t* b_q, GemmPar
   const bool column_factor = block && !p.exact && !p.dump && !scalar_factor && p.a_kind == I8L_ASCALE_TILE &&
                              p.b_kind != I8L_BSCALE_CHANNEL;
   if (!block) return two ? launch_kind<K_ROWCOL, true>(ma, mb, p, tiles, st) : launch_kind<K_ROWCOL, false>(ma, mb, p, tiles, st);
-  if (scalar_factor && p.a_kind == I8L_ASCALE_TILE) return launch_kind<K_BLOCK_FAST, false>(ma, mb, p, tiles, st);
+  // the fast kind encodes a sign in its factors: it needs them positive (scales are; post_scale must be too)
+  if (scalar_factor && p.a_kind == I8L_ASCALE_TILE && p.post_scale > 0.f) return launch_kind<K_BLOCK_FAST, false>(ma, mb, p, tiles, st);
   if (scalar_factor) return launch_kind<K_BLOCK_ROWFAC, false>(ma, mb, p, tiles, st);
   if (column_factor) return launch_kind<K_BLOCK_COLFAC, false>(ma, mb, p, tiles, st);
   return launch_kind<K_BLOCK_GEN, false>(ma, mb, p, tiles, st);
@@ -1114,6 +1180,12 @@ extern "C" int i8l_sum_slots(const void* slots, void* out, int world, int64_t ro
   sum_slots_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(slots),
                                                                         static_cast<uint4*>(out), world, n16);
   I8L_CUDA_OK(cudaGetLastError());
+  return I8L_OK;
+}
+
+extern "C" int i8l_set_cta_limit(int max_ctas) {
+  if (max_ctas < 0) return fail(I8L_ERR_ARG, "i8l_set_cta_limit: max_ctas must be >= 0");
+  g_cta_limit = max_ctas;
   return I8L_OK;
 }
 

@@ -454,6 +454,185 @@ quant_tile_hadrows_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Both rotated operands of a 128x128 tile from ONE read of x: q (rotation along the columns, as
+// quant_tile_hadcols_kernel) and qt (the transpose, rotation along the rows, as quant_tile_hadrows_kernel),
+// each with its own per-tile scale.  Results are bit-identical to those two kernels.
+//   Phase A: hadcols thread mapping; every 16-byte piece is also parked in shared memory as raw bf16.
+//   Phase B: thread (c, h) owns column c and the 64 rows whose bit 1 equals h (rows 4m+2h, 4m+2h+1), so
+//   that the butterfly of span 2 is the one that crosses the lane pair and the two lanes read different
+//   shared-memory banks; spans run in the order 1, 2, 4, ... 64 like everywhere else.  The quantized byte
+//   pairs are exchanged once more so that each lane stores 64 contiguous bytes of output row c.
+// ------------------------------------------------------------------------------------------------
+template <int MODE>
+__global__ void __launch_bounds__(256, 3)
+quant_tile_had_dual_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int64_t cols,
+                           int8_t* __restrict__ q, float* __restrict__ scale, int8_t* __restrict__ qt,
+                           float* __restrict__ scale_t) {
+  constexpr int LDB = 272;  // bytes per shared row: 256 + 16 (keeps 16-byte alignment, spreads the banks)
+  __shared__ __align__(16) uint8_t s_raw[128 * LDB];
+  __shared__ float s_red[8], s_red_t[8];
+  const int tid = threadIdx.x, w = tid >> 5, l = tid & 31, j4 = l & 3, rq = l >> 2;
+  const int64_t r_base = (int64_t)blockIdx.y * 128, c_base = (int64_t)blockIdx.x * 128;
+  const int64_t boff = (int64_t)blockIdx.z * rows * cols;
+  // ---------------------------------------------------------------- phase A: rotation along the columns
+  float s_tile = 0.f;
+  uint4 packed[2][4];
+  float tmax = 0.f;
+#pragma unroll
+  for (int it = 0; it < 2; ++it) {
+    const int r = 16 * w + 8 * it + rq;
+    const __nv_bfloat16* xr = x + boff + (r_base + r) * cols + c_base;
+    float2 pv[4][4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint4 u = __ldg(reinterpret_cast<const uint4*>(xr + 8 * (4 * c + j4)));
+      *reinterpret_cast<uint4*>(s_raw + r * LDB + 16 * (4 * c + j4)) = u;
+      float v[8];
+      unpack8(u, v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) pv[c][k] = make_float2(__fadd_rn(v[2 * k], v[2 * k + 1]), __fsub_rn(v[2 * k], v[2 * k + 1]));
+#pragma unroll
+      for (int h = 1; h < 4; h <<= 1)
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if ((k & h) == 0) {
+            const float2 a = pv[c][k], b = pv[c][k | h];
+            pv[c][k] = add2(a, b);
+            pv[c][k | h] = sub2(a, b);
+          }
+    }
+#pragma unroll
+    for (int m = 1; m < 4; m <<= 1) {
+      const float sg = (j4 & m) ? -1.f : 1.f;
+      const float2 sg2 = make_float2(sg, sg);
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 o = make_float2(__shfl_xor_sync(0xffffffffu, pv[c][k].x, m), __shfl_xor_sync(0xffffffffu, pv[c][k].y, m));
+          pv[c][k] = __ffma2_rn(pv[c][k], sg2, o);
+        }
+    }
+#pragma unroll
+    for (int h = 1; h < 4; h <<= 1)
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if ((c & h) == 0)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 a = pv[c][k], b = pv[c | h][k];
+            pv[c][k] = add2(a, b);
+            pv[c | h][k] = sub2(a, b);
+          }
+    __nv_bfloat162 hm = __floats2bfloat162_rn(0.f, 0.f);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed[it][c]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        h2[k] = __floats2bfloat162_rn(pv[c][k].x, pv[c][k].y);
+        hm = __hmax2(hm, __habs2(h2[k]));
+      }
+    }
+    tmax = fmaxf(tmax, fmaxf(__low2float(hm), __high2float(hm)));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+  if (l == 0) s_red[w] = tmax;
+  __syncthreads();   // also: the raw tile is complete in shared memory
+  tmax = s_red[0];
+#pragma unroll
+  for (int k = 1; k < 8; ++k) tmax = fmaxf(tmax, s_red[k]);
+  {
+    float stored;
+    make_scale<MODE>(tmax, s_tile, stored);
+    if (tid == 0) scale[((int64_t)blockIdx.z * (rows / 128) + blockIdx.y) * (cols / 128) + blockIdx.x] = stored;
+  }
+#pragma unroll
+  for (int it = 0; it < 2; ++it) {
+    const int r = 16 * w + 8 * it + rq;
+    int8_t* qr = q + boff + (r_base + r) * cols + c_base;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) *reinterpret_cast<uint2*>(qr + 8 * (4 * c + j4)) = quant_piece<MODE>(packed[it][c], s_tile);
+  }
+  // ---------------------------------------------------------------- phase B: rotation along the rows
+  const int c = tid >> 1, h = tid & 1;
+  float2 pv[32];   // pv[m] = rows 4m+2h, 4m+2h+1 of column c
+#pragma unroll
+  for (int m = 0; m < 32; ++m) {   // span 1 on the way in
+    const uint8_t* p0 = s_raw + (4 * m + 2 * h) * LDB + 2 * c;
+    const float a = bf16_bits_to_float(*reinterpret_cast<const uint16_t*>(p0));
+    const float b = bf16_bits_to_float(*reinterpret_cast<const uint16_t*>(p0 + LDB));
+    pv[m] = make_float2(__fadd_rn(a, b), __fsub_rn(a, b));
+  }
+  {   // span 2: the partner lane holds the rows with the other value of bit 1
+    const float sg = h ? -1.f : 1.f;
+    const float2 sg2 = make_float2(sg, sg);
+#pragma unroll
+    for (int m = 0; m < 32; ++m) {
+      const float2 o = make_float2(__shfl_xor_sync(0xffffffffu, pv[m].x, 1), __shfl_xor_sync(0xffffffffu, pv[m].y, 1));
+      pv[m] = __ffma2_rn(pv[m], sg2, o);   // own + partner, or partner - own
+    }
+  }
+#pragma unroll
+  for (int span = 1; span < 32; span <<= 1) {   // spans 4..64 of the rows = 1..16 of m
+#pragma unroll
+    for (int m = 0; m < 32; ++m) {
+      if ((m & span) == 0) {
+        const float2 a = pv[m], b = pv[m | span];
+        pv[m] = add2(a, b);
+        pv[m | span] = sub2(a, b);
+      }
+    }
+  }
+  uint32_t hv[32];
+  __nv_bfloat162 hm = __floats2bfloat162_rn(0.f, 0.f);
+#pragma unroll
+  for (int m = 0; m < 32; ++m) {
+    const __nv_bfloat162 b2 = __floats2bfloat162_rn(pv[m].x, pv[m].y);
+    hm = __hmax2(hm, __habs2(b2));
+    hv[m] = *reinterpret_cast<const uint32_t*>(&b2);
+  }
+  float mt = fmaxf(__low2float(hm), __high2float(hm));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, o));
+  if (l == 0) s_red_t[w] = mt;
+  __syncthreads();
+  mt = s_red_t[0];
+#pragma unroll
+  for (int k = 1; k < 8; ++k) mt = fmaxf(mt, s_red_t[k]);
+  float st, stored_t;
+  make_scale<MODE>(mt, st, stored_t);
+  if (tid == 0) scale_t[((int64_t)blockIdx.z * (cols / 128) + blockIdx.x) * (rows / 128) + blockIdx.y] = stored_t;
+  // quantize: byte pair m = (row 4m+2h, row 4m+2h+1) -> 16 bits; two pairs per 32-bit word
+  uint32_t pw[16];   // pw[i] = pair 2i | pair 2i+1 << 16
+  const float2 st2 = make_float2(st, st);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    int q0, q1, q2, q3;
+    quant2<MODE>(make_float2(__uint_as_float(hv[2 * i] << 16), __uint_as_float(hv[2 * i] & 0xffff0000u)), st2, q0, q1);
+    quant2<MODE>(make_float2(__uint_as_float(hv[2 * i + 1] << 16), __uint_as_float(hv[2 * i + 1] & 0xffff0000u)), st2, q2, q3);
+    pw[i] = pack4(q0, q1, q2, q3);
+  }
+  // lane h keeps the pairs of m in [16h, 16h+16) and receives the partner's pairs of the same m: output
+  // bytes 4m..4m+3 = (pair of lane 0, pair of lane 1)
+  uint32_t outw[16];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t send = h ? pw[i] : pw[8 + i];          // what the partner needs from this lane
+    const uint32_t got = __shfl_xor_sync(0xffffffffu, send, 1);
+    const uint32_t mine = h ? pw[8 + i] : pw[i];          // pairs 2i', 2i'+1 of the m range this lane writes
+    const uint32_t lo = h ? got : mine, hi = h ? mine : got;   // lane 0's pairs go to bytes 0-1, lane 1's to bytes 2-3
+    outw[2 * i] = __byte_perm(lo, hi, 0x5410);            // m = 2i':   lo.pair0 | hi.pair0 << 16
+    outw[2 * i + 1] = __byte_perm(lo, hi, 0x7632);        // m = 2i'+1: lo.pair1 | hi.pair1 << 16
+  }
+  int8_t* out = qt + boff + (c_base + c) * rows + r_base + 64 * h;
+#pragma unroll
+  for (int i = 0; i < 16; i += 4)
+    *reinterpret_cast<uint4*>(out + 4 * i) = make_uint4(outw[i], outw[i + 1], outw[i + 2], outw[i + 3]);
+}
+
 // Column absmax of x [rows, cols] into colmax[cols] (pre-zeroed); |x| >= 0 so the float bit
 // patterns order like integers and atomicMax on int is exact.
 __global__ void __launch_bounds__(256)
@@ -653,7 +832,10 @@ template <int GRAN, int MODE>
 static int dispatch_tile(const void* x, int64_t batch, int64_t rows, int64_t cols, bool had, int8_t* q,
                          float* scale, int8_t* qt, float* scale_t, const float* colmax, cudaStream_t st) {
   const bool n = q != nullptr, t = qt != nullptr;
-  if (had) {  // the two orientations rotate along different axes: one launch each
+  if (had && n && t && GRAN == I8L_GRAN_TILE128) {  // both rotated operands from one read of the tile
+    dim3 grid((unsigned)(cols / 128), (unsigned)(rows / 128), (unsigned)batch);
+    quant_tile_had_dual_kernel<MODE><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows, cols, q, scale, qt, scale_t);
+  } else if (had) {  // the two orientations rotate along different axes: one launch each
     if (n) {
       dim3 grid((unsigned)(cols / 128), (unsigned)(rows / 128), (unsigned)batch);
       quant_tile_hadcols_kernel<GRAN, MODE><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows, cols, q, scale);

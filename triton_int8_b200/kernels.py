@@ -209,3 +209,19 @@ def sum_slots(slots: torch.Tensor, out: torch.Tensor | None = None) -> torch.Ten
         out = torch.empty((rows, cols), dtype=torch.bfloat16, device=slots.device)
     _call("i8l_sum_slots", slots.device, slots.data_ptr(), out.data_ptr(), world, rows, cols, tensors=(out,))
     return out
+
+
+class cta_limit:
+    """Context manager: GEMMs launched inside use at most `n` CTAs, leaving the other SMs to a kernel
+    running beside them (a collective on another stream).  n <= 0 means no limit."""
+
+    def __init__(self, n: int):
+        self.n = max(0, int(n))
+
+    def __enter__(self):
+        L.call("i8l_set_cta_limit", self.n)
+        return self
+
+    def __exit__(self, *exc):
+        L.call("i8l_set_cta_limit", 0)
+        return False

@@ -79,10 +79,9 @@ def linear_forward(x2: torch.Tensor, weight: torch.Tensor, bias, cfg: Int8Config
     operand for dW (or None when want_xt is False)."""
     if cfg.whole_k:
         return _dc_forward(x2, weight, bias, cfg, want_xt)
-    fuse_t = want_xt and not cfg.hadamard
-    xq, xs, xqt, xst = K.quant_tile(x2[None], cfg.gran, cfg.qmode, cfg.hadamard, natural=True, transposed=fuse_t)
-    if want_xt and not fuse_t:  # the dW operand X^T is rotated along the tokens, not along K: second pass over X
-        _, _, xqt, xst = K.quant_tile(x2[None], cfg.gran, cfg.qmode, cfg.hadamard, natural=False, transposed=True)
+    # one call yields X (groups / rotation along K) and, for dW, X^T (along the tokens); with per-tile scales
+    # both come from a single read of X, rotated or not
+    xq, xs, xqt, xst = K.quant_tile(x2[None], cfg.gran, cfg.qmode, cfg.hadamard, natural=True, transposed=want_xt)
     wq, ws = K.quant_row(weight, cfg.qmode, cfg.hadamard)
     y = K.gemm_block(xq, wq, xs, ws, cfg.a_kind, L.BSCALE_CHANNEL, bias, cfg.post, cfg.flags)[0]
     return y, (xqt, xst)
@@ -117,11 +116,8 @@ def quantize_grad_output(dy2: torch.Tensor, cfg: Int8Config = DEFAULT, need_dx: 
         dy_op = K.quant_row(dy2[None], L.QMODE_ROWRCP, cfg.hadamard) if need_dx else (None, None)
         dyt_op = _dc_transposed(dy2, cfg) if need_dw else (None, None)
         return dy_op, dyt_op
-    fuse_t = need_dw and not cfg.hadamard
     dyq, dys, dyqt, dyst = K.quant_tile(dy2[None], cfg.gran, cfg.qmode, cfg.hadamard,
-                                        natural=need_dx, transposed=fuse_t)
-    if need_dw and not fuse_t:
-        _, _, dyqt, dyst = K.quant_tile(dy2[None], cfg.gran, cfg.qmode, cfg.hadamard, natural=False, transposed=True)
+                                        natural=need_dx, transposed=need_dw)
     return (dyq, dys), (dyqt, dyst)
 
 

@@ -134,18 +134,69 @@ class PeerSlots:
         return K.sum_slots(self.local, out)
 
 
+def gather_quantized_activations(x_rows: torch.Tensor, cfg: Int8Config = DEFAULT, group=None):
+    """Each rank holds only ITS M/g rows of the replicated activation X (e.g. the slice it copied from the
+    host): quantize them once, for both orientations, and all-gather the INT8 operands and their scales
+    over NVLink instead of moving bf16 X to every rank.  Per-tile scales are local to a 128-row block, so
+    the gathered operands equal bit for bit what every rank would have computed from the whole X.
+
+    x_rows bf16 [M/g, K] -> ((xq [1, M, K], xs [1, M/128, K/128]), (xqt [1, K, M], xst [1, K/128, M/128])):
+    the A operand of the forward GEMM and the saved B operand X^T of the dW GEMM.  tile128 scaling only.
+    """
+    if cfg.gran != L.GRAN_TILE128:
+        raise ValueError("gather_quantized_activations: per-tile (tile128) scaling only")
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    # both orientations from one read of the rows (128-token groups never straddle a rank's rows)
+    xq, xs, xqt, xst = K.quant_tile(x_rows[None], cfg.gran, cfg.qmode, cfg.hadamard, natural=True, transposed=True)
+    return gather_row_sharded_operands(xq, xs, xqt, xst, group)
+
+
+def gather_row_sharded_operands(xq, xs, xqt, xst, group=None):
+    """All-gather of operands quantized from a row shard of X: xq [1, M/g, K] and its tile scales
+    [1, M/g/128, K/128] concatenate along the rows in rank order; the transposed pieces xqt [1, K, M/g],
+    xst [1, K/128, M/g/128] sit side by side along the token axis of X^T."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        return (xq, xs), (xqt, xst)
+    _, Ml, Kd = xq.shape
+    M = Ml * world
+
+    def gather(t):   # [1, ..] local -> [world, ..]
+        out = torch.empty((world,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t.contiguous(), group=group)
+        return out
+    xq_all = gather(xq).view(1, M, Kd)
+    xs_all = gather(xs).view(1, M // 128, Kd // 128)
+    xqt_all = gather(xqt).permute(1, 0, 2).reshape(1, Kd, M)
+    xst_all = gather(xst).permute(1, 0, 2).reshape(1, Kd // 128, M // 128)
+    return (xq_all, xs_all), (xqt_all, xst_all)
+
+
 class ColumnParallelStep:
     """Forward + backward of one column-parallel linear with the dX reduce-scatter overlapped
     with the dW GEMM.  Holds the side stream and events; reuse one instance per layer."""
 
-    def __init__(self, group=None, cfg: Int8Config = DEFAULT, peer_slots: PeerSlots | None = None):
+    def __init__(self, group=None, cfg: Int8Config = DEFAULT, peer_slots: PeerSlots | None = None, comm_sms: int = 16):
         self.group, self.cfg = group, cfg
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.comm_stream = torch.cuda.Stream() if self.world > 1 else None
+        # The GEMMs are persistent, one CTA per SM; the dW GEMM that runs beside the reduce-scatter leaves
+        # `comm_sms` SMs to the collective's CTAs (otherwise NCCL's kernel waits for the GEMM to end).
+        sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        self.dw_ctas = max(1, sms - comm_sms) if (self.world > 1 and comm_sms > 0) else 0
         self.peer_slots = peer_slots   # when given, the dX GEMM scatters its partials itself (no NCCL reduce-scatter)
 
     def forward(self, x: torch.Tensor, w_shard: torch.Tensor, bias_shard=None):
         return linear_forward(x, w_shard, bias_shard, self.cfg, want_xt=True)
+
+    def forward_sharded(self, x_rows: torch.Tensor, w_shard: torch.Tensor, bias_shard=None):
+        """As forward(), from this rank's M/g rows of X only: the int8 operands are all-gathered
+        (gather_quantized_activations).  Returns (y [M, N/g], saved X^T operand)."""
+        cfg = self.cfg
+        (xq, xs), saved = gather_quantized_activations(x_rows, cfg, self.group)
+        wq, ws = K.quant_row(w_shard, cfg.qmode, cfg.hadamard)
+        y = K.gemm_block(xq, wq, xs, ws, cfg.a_kind, L.BSCALE_CHANNEL, bias_shard, cfg.post, cfg.flags)[0]
+        return y, saved
 
     def backward(self, dy_shard: torch.Tensor, w_shard: torch.Tensor, saved_xt):
         """Returns (dx rows owned by this rank [M/g, K], dw_shard [N/g, K])."""
@@ -162,6 +213,7 @@ class ColumnParallelStep:
         with torch.cuda.stream(self.comm_stream):
             dx = reduce_scatter_rows(dx_partial, self.group)
             dx_partial.record_stream(self.comm_stream)
-        dw = grad_weight(dyt_op, saved_xt, self.cfg)
+        with K.cta_limit(self.dw_ctas):
+            dw = grad_weight(dyt_op, saved_xt, self.cfg)
         main.wait_stream(self.comm_stream)
         return dx, dw
