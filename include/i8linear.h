@@ -167,6 +167,24 @@ I8L_API int i8l_gemm_block(const int8_t* a_q, const int8_t* b_q, const float* a_
                    int flags, int32_t* status, void* stream);
 
 /*
+ * The fused variant as ONE kernel, bf16 in and bf16 (or fp32) out: per 128 x 128 output tile and 128-wide K
+ * step the A tile and the B tile are read as bf16, scaled by 127 / (amax + 1e-5) (A: per 128 x 128 tile;
+ * B: per row and K step when b_batched == 0, per 128 x 128 tile when b_batched == 1), rounded with
+ * floor(x*s + 0.5) into the tensor core's shared-memory stage, multiplied exactly in int32
+ * (tcgen05.mma kind::i8) and accumulated as acc += float(P) / (s_a * s_b); no int8 tensor or scale is written
+ * to global memory.  Same integers, scales and results as i8l_quant_tile(I8L_QMODE_FUSED) on each operand
+ * followed by i8l_gemm_block(I8L_GEMM_DIVIDE); the quantization work is repeated for every output tile that
+ * consumes an operand tile, as in the reference.
+ *   a bf16 [batch, M, K]; b bf16 [N, K] (b_batched = 0) or [batch, N, K] (b_batched = 1); c [batch, M, N].
+ *   flags: I8L_GEMM_EXACT_ORDER (a true division per element and unfused adds: the reference's fp32 result
+ *   bit for bit; otherwise a multiplication by the rounded reciprocal of s_a*s_b), I8L_GEMM_OUT_F32.
+ * Replaces fused_int8_gemm_kernel and its launcher: triton/fused_triton_fwd32.py:23-96,
+ * triton/fused_triton_bwd33.py:24-86.
+ */
+I8L_API int i8l_fused_gemm(const void* a_bf, const void* b_bf, void* c, int64_t batch, int64_t M, int64_t N,
+                           int64_t K, int b_batched, int flags, int32_t* status, void* stream);
+
+/*
  * Row x column scaled INT8 GEMM: int32 accumulation over the whole K in TMEM, then
  * C = bf16( bf16((float(acc) * a_scale[m]) * b_scale[n]) * post_scale + bias ).
  * The intermediate bf16 rounding reproduces the reference, which stores the GEMM result as bf16

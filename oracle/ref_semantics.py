@@ -142,7 +142,7 @@ def quant_token_rne(w: torch.Tensor):
 
 def quant_rowgroup128(x: torch.Tensor):
     """Per (row, 128-wide group) absmax with the live Triton arithmetic (true division,
-    round half up, clamp): the grouping of BASELINE config 1 combined with the rounding
+    round half up, clamp): the per-(row, 128) grouping of the 512x1024x1024 test configuration combined with the rounding
     of triton/block_channel_fwd32.py:181-192.
     """
     lead, K = x.shape[:-1], x.shape[-1]
@@ -340,7 +340,7 @@ def gemm_block_bwd(aq, bq, a_s, b_s) -> torch.Tensor:
 
 
 def gemm_block_general(aq, bq, a_s, b_s, a_group_m: int, b_kind: str) -> torch.Tensor:
-    """Generalisation used for the BASELINE wording of config 1 (row x 128 groups):
+    """Generalisation used for the per-(row, 128-K) grouping of the 512x1024x1024 configuration:
     a_s is [B,M/a_group_m,K/128] with a_group_m in {1,128}; b_kind 'channel' ([N] K-invariant),
     'tile' ([B?,N/128,K/128]) or 'rowgroup' ([N,K/128]).  Same operation order as above.
     bq is [N,K] (shared) or [B,N,K].

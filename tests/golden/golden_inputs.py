@@ -35,7 +35,7 @@ def make_inputs(case: str):
         a[0, 3] = 0.0
         a[1, 7, 100] = -300.0
         return a, _randn(g, 128, 2048, std=0.02), _randn(g, 2, 128, 2048)
-    if case == "c1":           # BASELINE config 1 shapes / distributions
+    if case == "c1":           # 512x1024x1024 configuration: X ~ N(0,1) with 8 outlier columns x20, W ~ N(0,0.02), dY ~ N(0,1e-3)
         g = torch.Generator().manual_seed(20260000)
         x = torch.randn(512, 1024, generator=g)
         cols = torch.randperm(1024, generator=g)[:8]

@@ -1,4 +1,4 @@
-"""Full-size runs of the BASELINE configurations on the GPU, checked through properties that do not
+"""Full-size runs of the benchmark configurations on the GPU, checked through properties that do not
 need a full CPU recomputation: quantisation groups are local (a row, or a 128x128 tile), so the oracle
 evaluated on a slice of rows / tiles must reproduce the same slice of the full-size GPU result."""
 import pytest

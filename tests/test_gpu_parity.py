@@ -180,7 +180,7 @@ def test_block_channel_exact_mode_equals_reference_kernels(golden_dir, case):
 
 
 def test_block_channel_config1_both_wordings():
-    """BASELINE config 1 (512x1024x1024, outlier columns): reference scaling (tile128, half up) and the
+    """The 512x1024x1024 configuration (8 outlier columns): reference scaling (tile128, half up) and the
     per-(row,128)/RNE wording, forward + dX + dW by composition of the two primitives."""
     a, w, dy = make_inputs("c1")
     x = a[0]
@@ -377,3 +377,27 @@ def test_fast_block_epilogue_accuracy_deep_k(spread):
         ref2 += P * a_s[0, :, kb].double().repeat_interleave(128).view(M, 1) * b_t[:, kb].double().repeat_interleave(128).view(1, N)
     fast2 = K.gemm_block(args[0], args[1], args[2], b_t.to(DEV), b_kind=L.BSCALE_TILE, flags=L.GEMM_OUT_F32)[0].cpu().double()
     assert R.rel_fro(fast2, ref2) < 1e-4
+
+
+def test_single_kernel_fused_matches_reference_kernels(golden_dir):
+    """i8l_fused_gemm: bf16 in, result out, operand tiles quantized inside the GEMM.  Reference operation
+    order: bit-equal to the reference's fused kernels (golden); default order: equal to the two-step path."""
+    g = _golden(golden_dir, "fused_small")
+    a, w, b3 = make_inputs("small")
+    ad, wd, bd = a.to(DEV), w.to(DEV), b3.to(DEV)
+    _same(FU.fused_int8_gemm(ad, wd, out_dtype=torch.float32, exact=True, single_kernel=True), g["c_fwd"], "single-kernel fwd fp32")
+    _same(FU.fused_int8_gemm(ad, bd, out_dtype=torch.float32, exact=True, single_kernel=True), g["c_bwd"], "single-kernel bwd fp32")
+    for other in (wd, bd):
+        one = FU.fused_int8_gemm(ad, other, out_dtype=torch.float32, single_kernel=True)
+        two = FU.fused_int8_gemm(ad, other, out_dtype=torch.float32)
+        assert R.rel_fro(one.cpu(), two.cpu()) < 1e-6
+        assert torch.equal(FU.fused_int8_gemm(ad, other, single_kernel=True), FU.fused_int8_gemm(ad, other).to(torch.bfloat16)) or \
+            R.rel_fro(FU.fused_int8_gemm(ad, other, single_kernel=True).cpu().float(), two.cpu()) < TOL_BF16
+    # a shape with more tiles than SMs and a deeper K, against the exact product (the reference's gate)
+    gen = torch.Generator().manual_seed(9)
+    a2 = torch.randn(1, 2048, 2048, generator=gen).to(torch.bfloat16).to(DEV)
+    w2 = torch.randn(1536, 2048, generator=gen).to(torch.bfloat16).to(DEV)
+    y = FU.fwd_32(a2, w2, single_kernel=True)
+    assert FU.calc_diff(y, torch.matmul(a2, w2.t())) < 1e-3
+    assert R.rel_fro(y.cpu().float(), FU.fwd_32(a2, w2).cpu().float()) < 1e-2
+    K.check_status(DEV)

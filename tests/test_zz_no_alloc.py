@@ -44,6 +44,22 @@ def test_static_scratch_variant_matches_regular_entry_point_twice():
         assert torch.equal(s, s_ref), "scales differ from i8l_quant_col_t (bit-exact expected)"
 
 
+def test_static_scratch_variant_at_the_size_limit_and_against_the_oracle():
+    """cols == 65536, the largest the built-in scratch admits, and the values themselves against the CPU
+    restatement of the per-channel quantizer applied to x^T (not only against the sibling entry point)."""
+    from oracle import ref_semantics as R
+    from triton_int8_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(78)
+    x = (torch.randn(128, 65536, device=dev, generator=g) * 2.0).to(torch.bfloat16)
+    x[5, 40000] = 77.0
+    q, s = _call(lib, "static", x)
+    torch.cuda.synchronize()
+    q_ref, s_ref = R.quant_token(x.cpu().t().contiguous())
+    assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref.view(-1))
+
+
 def test_static_scratch_variant_rejects_oversize():
     from triton_int8_b200 import _lib
     lib = _lib.load()

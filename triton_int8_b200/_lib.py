@@ -32,6 +32,7 @@ SIGNATURES = {
     "i8l_quant_col_t_rot": [_P, _I64, _I64, _I, _P, _P, _P, _P],
     "i8l_gemm_block": [_P, _P, _P, _P, _I, _I, _I, _P, _F, _P, _I64, _I64, _I64, _I64, _I, _P, _P],
     "i8l_gemm_rowcol": [_P, _P, _P, _P, _I, _P, _F, _P, _I64, _I64, _I64, _I64, _I, _P, _P],
+    "i8l_fused_gemm": [_P, _P, _P, _I64, _I64, _I64, _I64, _I, _I, _P, _P],
     "i8l_gemm_dump_i32": [_P, _P, _I, _P, _I64, _I64, _I64, _I64, _I, _P, _P],
     "i8l_gemm_block_scatter": [_P, _P, _P, _P, _I, _F, _P, _I, _I, _I64, _I64, _I64, _P, _P],
     "i8l_sum_slots": [_P, _P, _I, _I64, _I64, _P],

@@ -14,6 +14,12 @@ int fail(int code, const char* fmt, ...);
 // I8L_OK when the current device is compute capability 10.x.
 int check_arch();
 
+// Shared launch settings of the tensor-core kernels (defined next to the GEMM launcher): the poll limit of
+// the bounded device-side waits (lowered only by the test hook) and the number of CTAs a persistent kernel
+// launched by this host thread may use (i8l_set_cta_limit, else the SM count).
+uint32_t gemm_wait_limit();
+int gemm_cta_budget();
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 #define I8L_CUDA_OK(expr)                                                                  \

@@ -29,6 +29,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace i8l {
 
@@ -79,164 +80,6 @@ struct GemmParams {
   int withhold;        // test hook: the producer leaves out the last operand load of its first tile
 };
 
-// ------------------------------------------------------------------------------------------ PTX
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// One poll: returns when the phase has completed or after the hardware's own time limit.  HINT adds
-// a suspend-time hint operand: it measured 1.3 % faster for the whole-K kernels (long waits by idle
-// warps) and 1 % slower for the block-scaled ones (short waits on the critical path).
-template <bool HINT>
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  if (HINT) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(1000000u)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-  }
-  return ok;
-}
-// Bounded wait.  A poll whose phase is incomplete parks the thread in hardware (about 4 us on a
-// B200, whatever suspend-time hint is given) and returns early when the phase completes, so a wait
-// is one instruction in the common case and the loop below runs only for waits longer than that.
-// The limit is a poll count (2^19 polls, about 2 s): no timer, no 64-bit arithmetic in the hot loops.
-// Returns false when the limit is hit or another warp has set the abort flag.
-constexpr uint32_t WAIT_MAX_POLLS = 1u << 19;
-template <bool HINT = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          uint32_t max_polls = WAIT_MAX_POLLS) {
-  if (mbar_try_wait<HINT>(bar, parity)) return true;
-  for (uint32_t spin = 1; spin < max_polls; ++spin) {
-    if (mbar_try_wait<HINT>(bar, parity)) return true;
-    if ((spin & 63u) == 0 && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-// The same bound for a caller that cannot leave its loop: returns when the phase has completed, or after
-// the limit with the abort flag set; once the flag is set (by any warp) a wait gives up after one poll.
-template <bool HINT = false>
-__device__ __forceinline__ void mbar_wait_or_flag(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                                  uint32_t max_polls = WAIT_MAX_POLLS) {
-  if (mbar_try_wait<HINT>(bar, parity)) return;
-  for (uint32_t spin = 1; spin < max_polls; ++spin) {
-    if (*abort_flag) return;
-    if (mbar_try_wait<HINT>(bar, parity)) return;
-  }
-  *abort_flag = 1;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
-// --- CTA-pair (cta_group::2) variants ---------------------------------------------------------
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// TMA load whose completion is signalled on a barrier of either CTA of the pair (no multicast).
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {  // arrives on `bar` in both CTAs of the pair
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               ::"r"(bar), "h"((uint16_t)3)
-               : "memory");
-}
-__device__ __forceinline__ void tc_commit_pair_local(uint32_t bar) {  // arrives on the executing CTA's barrier only
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_i8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                               uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t* r) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr)
-               : "memory");
-}
-__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void named_sync(int id, int nthreads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major operand, rows of 128 bytes, 128-byte swizzle,
-// 8-row groups 1024 bytes apart (the layout TMA writes with CU_TENSOR_MAP_SWIZZLE_128B).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
-  uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)1 << 16;              // leading byte offset (unused with swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;    // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;              // descriptor version for sm_100
-  d |= (uint64_t)2 << 61;              // SWIZZLE_128B
-  return d;
-}
 // Instruction descriptor: D=s32, A=B=s8, both K-major, M=128, N=256, dense, no saturation.
 constexpr uint32_t IDESC_I8 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
                               ((uint32_t)(BM >> 4) << 24);
@@ -258,14 +101,17 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int m_units, const GemmPa
   return tc;
 }
 
-struct __align__(8) SharedCtl {
+struct __align__(8) SharedCtl {   // tempty must directly follow tfull (the fast epilogue addresses both from one base)
   uint64_t full[MAX_STAGES], empty[MAX_STAGES], tfull[2], tempty[2], done;
+  uint64_t fready[2], ffree[2];  // fast block kind: factor buffers written (factor warp) / consumed (every epilogue thread)
   uint32_t tmem_base;
   int abort_flag;
   float bscale[EPI_WARPS / 4][EPI_COLS];     // per-tile column scales of each epilogue group (CHANNEL)
   float bstep[EPI_WARPS / 4][2][EPI_COLS];   // per-K-block column scales (GROUP), double buffered
-  float fac[EPI_WARPS / 4][FAC_MAX];         // per-K-block scalar factors of the current tile (K_BLOCK_FAST), signed
-  float fbias[EPI_WARPS / 4][2];             // running sum of the signed factors of the current tile (value, error term)
+  // K_BLOCK_FAST, written by the factor warp one unit (tile, or 512-K-block chunk of a tile) ahead, two buffers:
+  float fac[2][EPI_WARPS / 4][FAC_MAX];      // signed per-K-block scalar factors
+  float fbscale[2][EPI_WARPS / 4][EPI_COLS]; // per-channel column scales (times post_scale)
+  float fbias[2][EPI_WARPS / 4][2];          // running sum of the signed factors of the tile (value, error term)
 };
 
 // Epilogue kinds.  Everything but K_ROWCOL drains the accumulator every 128-wide K block.
@@ -384,6 +230,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       mbar_init(smem_u32(&ctl.tempty[b]), KIND == K_BLOCK_FAST ? EPI_WARPS * 32 : (TWO ? 2 : 1) * EPI_WARPS);
     }
     mbar_init(smem_u32(&ctl.done), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctl.fready[b]), 1);
+      mbar_init(smem_u32(&ctl.ffree[b]), EPI_WARPS * 32);
+    }
     ctl.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -423,7 +273,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int KB = p.KB;
 
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
     if (warp == 0) {
       // ------------------------------------------------------------------ TMA producer
       int s = 0;
@@ -517,6 +367,58 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       __syncwarp();
       int dummy = 0;
       mbar_wait(smem_u32(&ctl.done), 0, &dummy);
+    } else if (KIND == K_BLOCK_FAST && warp == 2) {
+      // ------------------------------------------------------------------ factor warp (fast block kind)
+      // Prepares, one unit ahead of the epilogue, what the epilogue needs besides the accumulators: the
+      // signed factor of every K block and the column scales.  Block d contributes g_d * (MAGIC_F + s_d P_d)
+      // with g_d = s_d f_d (see the epilogue), so the accumulators carry MAGIC_F * sum(g) on top of sum(f P).
+      // Choosing s_d against the sign of the running sum keeps |sum(g)| <= max f whatever the scales are, which
+      // bounds the rounding error the bias can cause; the epilogue takes the sum out after the last K block.
+      // Hand-over through two mbarrier pairs (buffer written / buffer consumed), waits bounded like all others.
+      const bool chan = p.b_kind == I8L_BSCALE_CHANNEL;
+      float run = 0.f, low = 0.f;   // lanes 0-3: the running sum of column group `lane` as an unevaluated pair
+      uint32_t u = 0;
+      for (int t = I8L_UNIT; t < total_tiles; t += I8L_N_UNITS) {
+        const TileCoord tc = unit_tile(t);
+        for (int k0 = 0; k0 < KB; k0 += FAC_MAX, ++u) {
+          const int dn = KB - k0 < FAC_MAX ? KB - k0 : FAC_MAX;
+          const int buf = u & 1;
+          if (u >= 2 && !mbar_wait(smem_u32(&ctl.ffree[buf]), ((u >> 1) - 1) & 1u, abort_flag, p.max_polls)) {
+            t = total_tiles;   // gave up (or another warp did): leave both loops
+            break;
+          }
+          for (int g = 0; g < EPI_WARPS / 4; ++g) {
+            const int col0 = tc.n_tile * BN + g * EPI_COLS;
+            const bool active = col0 < p.N;
+            const int64_t bcol0 = (int64_t)(p.b_batched ? tc.m_blk / p.mpb : 0) * p.N + col0;
+            if (chan)   // post_scale rides on the column scale (on the factors otherwise)
+              for (int i = lane; i < EPI_COLS; i += 32)
+                ctl.fbscale[buf][g][i] = active ? __ldg(p.b_scale + bcol0 + i) * p.post_scale : 0.f;
+            const float* as_ptr = p.a_scale + (int64_t)tc.m_blk * (KB >> p.a_kshift);
+            const float* bs_ptr = p.b_scale + (bcol0 >> 7) * KB + k0;
+            for (int i = lane; i < dn; i += 32)
+              ctl.fac[buf][g][i] = __ldg(as_ptr + ((k0 + i) >> p.a_kshift)) * ((!chan && active) ? __ldg(bs_ptr + i) * p.post_scale : 1.f);
+          }
+          __syncwarp();
+          if (lane < EPI_WARPS / 4) {
+            if (k0 == 0) run = low = 0.f;
+            float* f = ctl.fac[buf][lane];
+            for (int i = 0; i < dn; ++i) {
+              float g = f[i];
+              g = run > 0.f ? -g : g;
+              const float sum = __fadd_rn(run, g);
+              const float bb = __fsub_rn(sum, run);   // two-sum: the rounding error of run + g, off the critical chain
+              low = __fadd_rn(low, __fadd_rn(__fsub_rn(run, __fsub_rn(sum, bb)), __fsub_rn(g, bb)));
+              run = sum;
+              f[i] = g;
+            }
+            ctl.fbias[buf][lane][0] = run;
+            ctl.fbias[buf][lane][1] = low;
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ctl.fready[buf]));   // release: the warp's writes above are visible to waiters
+        }
+      }
     }
   } else {
     // -------------------------------------------------------------------- epilogue (16 warps)
@@ -540,75 +442,48 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // per-channel B scale.  The K-block loop keeps only the accumulators, one chunk of tensor-memory
       // data and a few scalars live: the factors of the tile are staged in shared memory first, and
       // what the final store needs is recomputed from the tile index afterwards.
-      const uint32_t tfull0 = smem_u32(&ctl.tfull[0]), tempty0 = smem_u32(&ctl.tempty[0]);
+      const uint32_t tfull0 = smem_u32(&ctl.tfull[0]);
+      constexpr uint32_t TEMPTY_OFF = 2 * sizeof(uint64_t);   // tempty[] follows tfull[2] in SharedCtl: one base register serves both
       // Values derived from the thread index pass through an empty asm statement: the compiler then
       // keeps them in registers instead of recomputing them from the special register at every use
       // inside the K-block loop (which cost about 35 ALU instructions per warp and K block).
-      uint32_t taddr0 = tmem_base + lane_addr + wg * EPI_COLS, fac0 = smem_u32(&ctl.fac[wg][0]);
-      asm volatile("" : "+r"(taddr0), "+r"(fac0));
+      uint32_t taddr0 = tmem_base + lane_addr + wg * EPI_COLS, fac_base = smem_u32(&ctl.fac[0][wg][0]);
+      asm volatile("" : "+r"(taddr0), "+r"(fac_base));
       const bool chan = p.b_kind == I8L_BSCALE_CHANNEL;
       constexpr int CH = 8;
-      uint32_t gstep = 0;
-      // The loops below never exit early: the warps of a column group meet at named barriers, so after a
-      // wait timeout (`ok` false) a warp runs through the remaining tiles without waiting or computing.
+      uint32_t gstep = 0, unit = 0;
+      // The loops below never exit early (one exit and nothing to carry but the accumulators compiles to the
+      // leanest code): after a wait timeout a warp runs through the remaining tiles without waiting or storing.
       for (int t = I8L_UNIT; t < total_tiles; t += I8L_N_UNITS) {
         float2 acc[EPI_COLS / 2];
 #pragma unroll
         for (int j = 0; j < EPI_COLS / 2; ++j) acc[j] = make_float2(0.f, 0.f);
-        bool active = true;
+        const bool active = unit_tile(t).n_tile * BN + wg * EPI_COLS < p.N;
         for (int k0 = 0; k0 < KB; k0 += FAC_MAX) {
           const int dn = KB - k0 < FAC_MAX ? KB - k0 : FAC_MAX;
-          {
-            const TileCoord tc = unit_tile(t);
-            const int col0 = tc.n_tile * BN + wg * EPI_COLS;
-            active = col0 < p.N;
-            const int64_t bcol0 = (int64_t)(p.b_batched ? tc.m_blk / p.mpb : 0) * p.N + col0;
-            named_sync(1 + wg, 128);  // the group is done with the previous contents
-            if (k0 == 0 && chan && tix < EPI_COLS)  // post_scale rides on the column scale (on the factors otherwise)
-              ctl.bscale[wg][tix] = active ? __ldg(p.b_scale + bcol0 + tix) * p.post_scale : 0.f;
-            const float* as_ptr = p.a_scale + (int64_t)tc.m_blk * (KB >> p.a_kshift);
-            const float* bs_ptr = p.b_scale + (bcol0 >> 7) * KB + k0;
-            for (int i = tix; i < dn; i += 128)
-              ctl.fac[wg][i] = __ldg(as_ptr + ((k0 + i) >> p.a_kshift)) * ((!chan && active) ? __ldg(bs_ptr + i) * p.post_scale : 1.f);
-            named_sync(1 + wg, 128);
-            // Signs for the biased conversion (see the K-block loop): block d contributes g_d * (MAGIC_F + s_d P_d)
-            // with g_d = s_d f_d, so the accumulators carry MAGIC_F * sum(g) on top of sum(f P).  Choosing s_d
-            // against the sign of the running sum keeps |sum(g)| <= max f whatever the scales are, which bounds the
-            // rounding error the bias can cause; the sum is taken out again after the last K block.
-            if (tix == 0) {
-              // the sum as an unevaluated pair (run, low): its error times MAGIC_F would otherwise show in the result
-              float run = k0 == 0 ? 0.f : ctl.fbias[wg][0], low = k0 == 0 ? 0.f : ctl.fbias[wg][1];
-              for (int i = 0; i < dn; ++i) {
-                float g = ctl.fac[wg][i];
-                g = run > 0.f ? -g : g;
-                const float sum = __fadd_rn(run, g);
-                const float bb = __fsub_rn(sum, run);   // two-sum: the rounding error of run + g, off the critical chain
-                low = __fadd_rn(low, __fadd_rn(__fsub_rn(run, __fsub_rn(sum, bb)), __fsub_rn(g, bb)));
-                run = sum;
-                ctl.fac[wg][i] = g;
-              }
-              ctl.fbias[wg][0] = run;
-              ctl.fbias[wg][1] = low;
-            }
-            named_sync(1 + wg, 128);
+          if (k0) {   // the previous chunk's factors are no longer needed
+            mbar_arrive(smem_u32(&ctl.ffree[unit & 1]));
+            ++unit;
           }
+          mbar_wait_or_flag(smem_u32(&ctl.fready[unit & 1]), (unit >> 1) & 1u, abort_flag, p.max_polls);   // written by the factor warp
+          const uint32_t fac0 = fac_base + (unit & 1) * (uint32_t)sizeof(ctl.fac[0]);
           for (int d = 0; d < dn; ++d) {
             float f;
             asm volatile("ld.shared.f32 %0, [%1];" : "=f"(f) : "r"(fac0 + 4 * d));
             // No early exit and no success flag: a loop with one exit and nothing to carry but the
             // accumulators compiles to the leanest code.  After a timeout the abort flag is set, the status
             // word reports it, and the remaining K blocks run on whatever tensor memory holds.
-            mbar_wait_or_flag(tfull0 + 8 * ab, aph, abort_flag, p.max_polls);
+            mbar_spin_or_flag(tfull0 + 8 * ab, aph, abort_flag, p.max_polls);
             tc_fence_after();
             auto release = [&]() {  // all of this warp's tensor-memory loads of the buffer have completed
               tc_fence_before();
-              mbar_arrive(tempty0 + 8 * ab);   // every thread arrives for itself: no warp sync, no branch
+              mbar_arrive(tfull0 + TEMPTY_OFF + 8 * ab);   // every thread arrives for itself: no warp sync, no branch
             };
             if (active) {
               // int32 -> fp32 without the conversion unit: |P| <= 128*127*127 < 2^22, so the integer MAGIC_I + P
               // (or MAGIC_I - P), read as a float, IS the number 1.5*2^23 + P (or - P): one full-rate integer
               // add per element instead of a half-rate conversion.  The factor carries the sign, so the product
-              // is f*P plus a multiple of MAGIC_F that the staging code keeps small and the tile end removes.
+              // is f*P plus a multiple of MAGIC_F that the factor warp keeps small and the tile end removes.
               const uint32_t taddr = taddr0 + ab * BN;
               const float2 f2 = make_float2(f, f);
               if (f >= 0.f) {
@@ -650,8 +525,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const TileCoord tc = unit_tile(t2);
           // take out MAGIC_F * sum(g): the leading part first (close to the accumulator, so the difference is
           // nearly exact), then the small remainder
-          const float b_hi = __fmul_rn(-MAGIC_F, ctl.fbias[wg][0]);
-          const float b_lo = __fmaf_rn(-MAGIC_F, ctl.fbias[wg][0], -b_hi) + __fmul_rn(-MAGIC_F, ctl.fbias[wg][1]);
+          const float* fb = ctl.fbias[unit & 1][wg];
+          const float b_hi = __fmul_rn(-MAGIC_F, fb[0]);
+          const float b_lo = __fmaf_rn(-MAGIC_F, fb[0], -b_hi) + __fmul_rn(-MAGIC_F, fb[1]);
           float out[EPI_COLS];
 #pragma unroll
           for (int j = 0; j < EPI_COLS / 2; ++j) {
@@ -665,8 +541,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             cbase = p.c_slots[owner];
             row += (int64_t)(p.rs_rank - owner) * p.rs_rows;
           }
-          store_cols<false>(p, out, chan ? ctl.bscale[wg] : nullptr, row, tc.n_tile * BN + wg * EPI_COLS, cbase);
+          store_cols<false>(p, out, chan ? ctl.fbscale[unit & 1][wg] : nullptr, row, tc.n_tile * BN + wg * EPI_COLS, cbase);
         }
+        mbar_arrive(smem_u32(&ctl.ffree[unit & 1]));   // this tile's factors and column scales are no longer needed
+        ++unit;
       }
     } else
     for (int t = I8L_UNIT; t < total_tiles; t += I8L_N_UNITS) {  // no early exit either (named barriers inside)
@@ -999,6 +877,15 @@ static thread_local int g_cta_limit = 0;
 static std::atomic<uint32_t> g_test_max_polls{0};
 static std::atomic<int> g_test_withhold{0};
 
+uint32_t gemm_wait_limit() {
+  const uint32_t lim = g_test_max_polls.load(std::memory_order_relaxed);
+  return lim ? lim : WAIT_MAX_POLLS;
+}
+int gemm_cta_budget() {
+  const int sms = sm_count();
+  return (g_cta_limit > 0 && g_cta_limit < sms) ? g_cta_limit : sms;
+}
+
 template <int KIND, bool TWO>
 static int launch_kind(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int64_t tiles, cudaStream_t st) {
   // per-device set-up, done by whichever thread comes first (idempotent, so a race only repeats it)
@@ -1065,8 +952,7 @@ static int launch_gemm(bool block, const int8_t* a_q, const int8_t* b_q, GemmPar
   p.N = (int)N;
   p.KB = (int)(K / 128);
   {
-    const uint32_t lim = g_test_max_polls.load(std::memory_order_relaxed);
-    p.max_polls = lim ? lim : WAIT_MAX_POLLS;
+    p.max_polls = gemm_wait_limit();
     p.withhold = g_test_withhold.load(std::memory_order_relaxed);
   }
   p.c_align32 = (reinterpret_cast<uintptr_t>(p.c) & 31u) == 0;

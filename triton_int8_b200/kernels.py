@@ -171,6 +171,22 @@ def gemm_rowcol(aq, bq, a_s, b_s, bias=None, post_scale=1.0, flags=0, status=Non
     return out
 
 
+def fused_gemm(a_bf, b_bf, flags=0, status=None):
+    """bf16 a [B, M, K] x bf16 b [N, K] or [B, N, K] -> bf16 (fp32 with GEMM_OUT_F32) [B, M, N] in ONE kernel:
+    operand tiles are quantized on the fly per 128-wide K step inside the GEMM (nothing int8 reaches memory)."""
+    a_bf, b_bf = _check_bf16(a_bf, "a"), _check_bf16(b_bf, "b")
+    B, M, K = a_bf.shape
+    bb = b_bf.dim() == 3
+    N = b_bf.shape[-2]
+    if b_bf.shape[-1] != K or (bb and b_bf.shape[0] != B):
+        raise ValueError(f"operand shapes do not match: {tuple(a_bf.shape)} x {tuple(b_bf.shape)}")
+    out = torch.empty((B, M, N), dtype=torch.float32 if flags & L.GEMM_OUT_F32 else torch.bfloat16, device=a_bf.device)
+    status = device_status(a_bf.device) if status is None else status
+    _call("i8l_fused_gemm", a_bf.device, a_bf.data_ptr(), b_bf.data_ptr(), out.data_ptr(), B, M, N, K, int(bb), flags,
+          _ptr(status), tensors=(b_bf, status))
+    return out
+
+
 def gemm_dump_i32(aq, bq, per_block=False, status=None):
     aq, bq = aq.contiguous(), bq.contiguous()
     B, M, N, K, bb = _gemm_dims(aq, bq)
