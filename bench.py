@@ -512,11 +512,16 @@ def main():
     Kn.check_status(dev)
     rows_y = slice(0, 256)
     y_ref = x[rows_y].float() @ w.float().t()
-    own0 = rank * (M // world)
-    rows_dx = slice(own0, own0 + 128)
-    dx_ref = dy[rows_dx].float() @ w.float()
+    # dX: rank r owns rows [r*M/g, (r+1)*M/g) after the reduce-scatter; the reference for ITS first 128 rows is the
+    # sum over all ranks q of dY_q[those rows] W_q, so every rank computes its partial for every owner's rows
+    own = [q * (M // world) for q in range(world)]
+    wf = w.float()
+    dx_parts = torch.stack([dy[o:o + 128].float() @ wf for o in own])
+    del wf
     if world > 1:
-        dist.all_reduce(dx_ref)
+        dist.all_reduce(dx_parts)
+    dx_ref = dx_parts[rank]
+    del dx_parts
     dw_ref = dy[:, :128].float().t() @ x[:, :256].float()
     par = {"y": (y[0, rows_y] if y.dim() == 3 else y[rows_y], y_ref),
            "dx": (dx[:128], dx_ref), "dw": (dw[:128, :256], dw_ref)}
@@ -579,8 +584,10 @@ def main():
     tr_ = time_fn(lambda: Kn.quant_row(w, L.QMODE_TRITON, 0))
     th = time_fn(lambda: Kn.quant_tile(dy[None], L.GRAN_TILE128, L.QMODE_TRITON, 128, natural=True, transposed=False))
     tht = time_fn(lambda: Kn.quant_tile(dy[None], L.GRAN_TILE128, L.QMODE_TRITON, 128, natural=False, transposed=True))
+    thd = time_fn(lambda: Kn.quant_tile(dy[None], L.GRAN_TILE128, L.QMODE_TRITON, 128, natural=True, transposed=True))
     E = dy.numel()
     quant = {
+        "tile128_had128_dual_gbs": 4 * E / thd / 1e6, "tile128_had128_dual_frac": 4 * E / thd / 1e6 / measured_peaks()[0]["hbm_gbs"],
         "tile128_had128_gbs": 3 * E / th / 1e6, "tile128_had128_transposed_gbs": 3 * E / tht / 1e6,
         "tile128_dual_out_gbs": (2 * E + 2 * E) / tq / 1e6, "tile128_gbs": (2 * E + E) / tq1 / 1e6,
         "row_gbs": 3 * w.numel() / tr_ / 1e6, "hbm_peak_gbs": measured_peaks()[0]["hbm_gbs"],
@@ -753,10 +760,22 @@ def main():
             "roofline": roofline, "targets": targets, "quantizers": quant, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": launches_per_step * args.steps, "clocks": clk.summary(),
         }))
+    sys.stdout.flush()
+    rc = 0 if parity["ok"] else 1
+    if rc:
+        print(f"[bench] rank {rank}: parity gate failed: {parity}", file=sys.stderr, flush=True)
+    # Teardown.  The captured graph holds the communicator's reduce-scatter: release it before the process
+    # group goes, and never let a stuck teardown keep a finished benchmark alive (a watchdog ends the process
+    # with the result's exit code).
+    threading.Timer(60.0, lambda: os._exit(rc)).start()
+    graph = None
+    e2e_obj = feed = None
+    torch.cuda.synchronize()
     if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
         dist.destroy_process_group()
-    if not parity["ok"]:
-        raise SystemExit(f"parity gate failed: {parity}")
+    os._exit(rc)
 
 
 if __name__ == "__main__":

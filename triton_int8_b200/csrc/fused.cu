@@ -4,8 +4,10 @@
 // scale of each operand tile it consumes and quantizes it on the fly, per 128-wide K step.
 //
 // One persistent CTA per SM, 640 threads, tile 128 x 128, K step 128:
-//   warps 12-19  transform: load the bf16 A tile (128 x 128) and B tile (128 x 128) of the K step from global
-//                memory (16-byte vectors, 16 lanes per 256-byte row), absmax per A tile and per B row (forward)
+//   warp 0       TMA producer: the bf16 A tile (128 x 128) and B tile (128 x 128) of every K step into a two-stage
+//                staging ring in shared memory (unswizzled 256-byte rows), so the loads run ahead of the math.
+//   warps 12-19  transform: read the staged tiles (16-byte vectors, 16 lanes per row) into registers and give
+//                the staging slot back at once; absmax per A tile and per B row (forward)
 //                or per B tile (backward), scale = 127 / (amax + 1e-5), q = floor(x * scale + 0.5), int8 written
 //                into the K-major 128B-swizzled shared-memory stage the tensor core reads, then
 //                fence.proxy.async and an arrival on the stage's "full" barrier; the step's scales go to a
@@ -31,12 +33,14 @@ namespace i8l {
 namespace fusedk {
 
 constexpr int TM = 128, TN = 128, TK = 128;
-constexpr int NS = 4;                       // int8 stages: 16 KB A + 16 KB B each
+constexpr int NS = 2;                       // int8 stages: 16 KB A + 16 KB B each
+constexpr int NB = 2;                       // bf16 staging slots: 32 KB A + 32 KB B each
 constexpr int STAGE_A = TM * TK, STAGE_B = TN * TK;
+constexpr int BF_A = TM * TK * 2, BF_B = TN * TK * 2;
 constexpr int RING = 8;                     // scale ring entries (a step's scales live until its drain)
 constexpr int THREADS = 640;
 constexpr int XF_WARP0 = 12, XF_THREADS = 256, EPI_THREADS = 256;
-constexpr int SMEM_DYN = NS * (STAGE_A + STAGE_B) + 1024;
+constexpr int SMEM_DYN = NS * (STAGE_A + STAGE_B) + NB * (BF_A + BF_B) + 1024;
 constexpr int TMEM_COLS = 256;
 constexpr int BAR_XF = 9;                   // named barrier of the transform warps
 constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
@@ -44,8 +48,6 @@ constexpr uint32_t MAGIC_I = 0x4B400000u;
 constexpr float MAGIC_F = 12582912.f;
 
 struct Params {
-  const __nv_bfloat16* a;   // [batch * M, K]
-  const __nv_bfloat16* b;   // [N, K] or [batch * N, K]
   void* c;
   int32_t* status;
   int64_t K;
@@ -55,7 +57,7 @@ struct Params {
 };
 
 struct __align__(8) Ctl {
-  uint64_t full[NS], empty[NS], tfull[2], tempty[2], sfull[RING], done;
+  uint64_t full[NS], empty[NS], bfull[NB], bempty[NB], tfull[2], tempty[2], sfull[RING], done;
   uint32_t tmem_base;
   int abort_flag;
   float red_a[2][8], red_b[2][8];   // per-warp absmax partials, double buffered over the K steps
@@ -67,11 +69,13 @@ __device__ __forceinline__ void st_shared_v2(uint32_t addr, uint2 v) {
   asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(v.x), "r"(v.y) : "memory");
 }
 
-__global__ void __launch_bounds__(THREADS, 1) fused_gemm_kernel(const Params p) {
+__global__ void __launch_bounds__(THREADS, 1)
+fused_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ Ctl ctl;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t smem_a = smem_base, smem_b = smem_base + NS * STAGE_A;
+  const uint32_t smem_bfa = smem_base + NS * (STAGE_A + STAGE_B), smem_bfb = smem_bfa + NB * BF_A;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &ctl.abort_flag;
 
@@ -79,6 +83,10 @@ __global__ void __launch_bounds__(THREADS, 1) fused_gemm_kernel(const Params p) 
     for (int s = 0; s < NS; ++s) {
       mbar_init(smem_u32(&ctl.full[s]), XF_THREADS);
       mbar_init(smem_u32(&ctl.empty[s]), 1);
+    }
+    for (int s = 0; s < NB; ++s) {
+      mbar_init(smem_u32(&ctl.bfull[s]), 1);
+      mbar_init(smem_u32(&ctl.bempty[s]), XF_THREADS);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctl.tfull[b]), 1);
@@ -88,6 +96,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_gemm_kernel(const Params p) 
     mbar_init(smem_u32(&ctl.done), 1);
     ctl.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl.tmem_base)), "r"(TMEM_COLS)
@@ -102,7 +111,36 @@ __global__ void __launch_bounds__(THREADS, 1) fused_gemm_kernel(const Params p) 
   const int KB = p.KB;
 
   if (warp < 4) {
-    if (warp == 1) {
+    if (warp == 0) {
+      // ------------------------------------------------------------------ TMA producer (bf16 staging)
+      int s = 0;
+      uint32_t ph = 0, issued = 0, issued_ph = 0;   // bit s: a load into slot s is (or was) in flight, with parity
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int m_blk = t % p.m_blocks, n_tile = t / p.m_blocks;
+        const int a_row = m_blk * TM;
+        const int b_row = (p.b_batched ? (m_blk / p.mpb) * p.N : 0) + n_tile * TN;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!(ok = mbar_wait(smem_u32(&ctl.bempty[s]), ph ^ 1u, abort_flag, p.max_polls))) break;
+          if (lane == 0) {
+            const uint32_t bar = smem_u32(&ctl.bfull[s]);
+            mbar_expect_tx(bar, BF_A + BF_B);
+            tma_load_2d(smem_bfa + s * BF_A, &map_a, bar, kb * TK, a_row);
+            tma_load_2d(smem_bfb + s * BF_B, &map_b, bar, kb * TK, b_row);
+          }
+          issued |= 1u << s;
+          issued_ph = (issued_ph & ~(1u << s)) | (ph << s);
+          if (++s == NB) { s = 0; ph ^= 1u; }
+        }
+      }
+      if (!ok) {   // let copies already in flight land before the CTA's shared memory is released
+        for (int k = 0; k < NB; ++k)
+          if (issued & (1u << k)) {
+            int dummy = 0;
+            mbar_wait(smem_u32(&ctl.bfull[k]), (issued_ph >> k) & 1u, &dummy, 1u << 15);
+          }
+      }
+    } else if (warp == 1) {
       // ------------------------------------------------------------------ MMA issuer
       int s = 0, ab = 0;
       uint32_t ph = 0, aph = 0;
@@ -214,29 +252,28 @@ __global__ void __launch_bounds__(THREADS, 1) fused_gemm_kernel(const Params p) 
   } else {
     // -------------------------------------------------------------------- transform (8 warps)
     const int tw = warp - XF_WARP0, cc = lane & 15, half = lane >> 4, xtid = tw * 32 + lane;
-    int s = 0;
-    uint32_t ph = 0, step = 0;
+    int s = 0, sb = 0;
+    uint32_t ph = 0, bph = 0, step = 0;
     bool ok = true;
     // No early exit: the eight warps meet at a named barrier every step, so after a timeout they run through
     // the remaining steps without loading, waiting or arriving.
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-      const int m_blk = t % p.m_blocks, n_tile = t / p.m_blocks;
-      const __nv_bfloat16* a0 = p.a + (int64_t)m_blk * TM * p.K;
-      const __nv_bfloat16* b0 = p.b + ((int64_t)(p.b_batched ? (m_blk / p.mpb) * p.N : 0) + (int64_t)n_tile * TN) * p.K;
       for (int kb = 0; kb < KB; ++kb, ++step) {
         uint4 ra[2][4], rb[2][4];
         const __nv_bfloat162 zero2 = __floats2bfloat162_rn(0.f, 0.f);
         __nv_bfloat162 ma = zero2, mbt = zero2;
         float rowmax[2][4];
+        ok = ok && mbar_wait(smem_u32(&ctl.bfull[sb]), bph, abort_flag, p.max_polls);   // the step's bf16 tiles have landed
         if (ok) {
 #pragma unroll
           for (int it = 0; it < 2; ++it)
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const int r = 16 * tw + 8 * it + 4 * half + i;
-              ra[it][i] = __ldg(reinterpret_cast<const uint4*>(a0 + (int64_t)r * p.K + (int64_t)kb * TK + 8 * cc));
-              rb[it][i] = __ldg(reinterpret_cast<const uint4*>(b0 + (int64_t)r * p.K + (int64_t)kb * TK + 8 * cc));
+              ra[it][i] = *reinterpret_cast<const uint4*>(smem_raw + (smem_bfa - smem_u32(smem_raw)) + sb * BF_A + r * 256 + 16 * cc);
+              rb[it][i] = *reinterpret_cast<const uint4*>(smem_raw + (smem_bfb - smem_u32(smem_raw)) + sb * BF_B + r * 256 + 16 * cc);
             }
+          mbar_arrive(smem_u32(&ctl.bempty[sb]));   // the tiles are in registers: the slot can be refilled
 #pragma unroll
           for (int it = 0; it < 2; ++it)
 #pragma unroll
@@ -303,6 +340,7 @@ __global__ void __launch_bounds__(THREADS, 1) fused_gemm_kernel(const Params p) 
           }
         }
         if (++s == NS) { s = 0; ph ^= 1u; }
+        if (++sb == NB) { sb = 0; bph ^= 1u; }
       }
     }
   }
@@ -333,8 +371,9 @@ extern "C" int i8l_fused_gemm(const void* a_bf, const void* b_bf, void* c, int64
   if (flags & ~(I8L_GEMM_EXACT_ORDER | I8L_GEMM_OUT_F32)) return fail(I8L_ERR_ARG, "i8l_fused_gemm: flags may hold EXACT_ORDER and OUT_F32");
   if (int e = check_arch()) return e;
   fusedk::Params p{};
-  p.a = static_cast<const __nv_bfloat16*>(a_bf);
-  p.b = static_cast<const __nv_bfloat16*>(b_bf);
+  CUtensorMap map_a, map_b;
+  if (int e = make_tile_map_bf16(&map_a, a_bf, batch * M, K)) return e;
+  if (int e = make_tile_map_bf16(&map_b, b_bf, b_batched ? batch * N : N, K)) return e;
   p.c = c;
   p.status = status;
   p.K = K;
@@ -359,7 +398,7 @@ extern "C" int i8l_fused_gemm(const void* a_bf, const void* b_bf, void* c, int64
   const int64_t tiles = (int64_t)p.m_blocks * p.n_tiles;
   const int ctas = gemm_cta_budget();
   const int grid = (int)(tiles < ctas ? tiles : ctas);
-  fusedk::fused_gemm_kernel<<<grid, fusedk::THREADS, fusedk::SMEM_DYN, static_cast<cudaStream_t>(stream)>>>(p);
+  fusedk::fused_gemm_kernel<<<grid, fusedk::THREADS, fusedk::SMEM_DYN, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, p);
   I8L_CUDA_OK(cudaGetLastError());
   return I8L_OK;
 }

@@ -852,6 +852,22 @@ static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, 
   return I8L_OK;
 }
 
+// bf16 [rows, K] row-major -> boxes of 128 rows x 128 elements (256-byte rows in shared memory, no swizzle):
+// the staging tiles of the single-kernel fused GEMM.
+int make_tile_map_bf16(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return fail(I8L_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t gstr[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {128, 128};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstr, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(I8L_ERR_CUDA, "cuTensorMapEncodeTiled (bf16) failed with CUresult %d", (int)r);
+  return I8L_OK;
+}
+
 constexpr int MAX_DEVICES = 64;
 static int current_device() {
   int dev = 0;

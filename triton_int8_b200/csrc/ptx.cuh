@@ -6,6 +6,10 @@
 
 namespace i8l {
 
+// Host: tensor map of a bf16 [rows, K] matrix in boxes of 128 x 128 elements, unswizzled (defined with the
+// other tensor-map code next to the GEMM launcher).
+int make_tile_map_bf16(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K);
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
