@@ -139,7 +139,11 @@ I8L_API int i8l_quant_col_t_static(const void* x, int64_t rows, int64_t cols, in
 
 #define I8L_GEMM_EXACT_ORDER 1 /* per K step evaluate (float(P)*a_s)*b_s then add, unfused: bit-equal to the
                                   reference's fp32 result.  Without it the K-invariant factor is applied once
-                                  at the end and multiply-adds are fused (same int32 partials). */
+                                  at the end, multiply-adds are fused and, for per-tile A scales with per-tile or
+                                  per-channel B scales, the int32 partials enter the fp32 sum through a bounded
+                                  bias that is removed at the end of the tile (same int32 partials; fp32 result
+                                  within 1e-4 relative of the exact sum at K = 32768, typically 1e-6; scale
+                                  products times 1.3e7 must stay finite in fp32). */
 #define I8L_GEMM_DIVIDE 2      /* scales are multipliers s: acc += float(P) / (a_s*b_s)  (fused variants); together with
                                   EXACT_ORDER a true division per element, otherwise a multiplication by the rounded
                                   reciprocal of a_s*b_s (differs from the division by at most 1 ulp per K block) */
