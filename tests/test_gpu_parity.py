@@ -401,3 +401,19 @@ def test_single_kernel_fused_matches_reference_kernels(golden_dir):
     assert FU.calc_diff(y, torch.matmul(a2, w2.t())) < 1e-3
     assert R.rel_fro(y.cpu().float(), FU.fwd_32(a2, w2).cpu().float()) < 1e-2
     K.check_status(DEV)
+
+
+def test_fast_block_epilogue_more_than_512_k_blocks():
+    """K = 73728 = 576 K blocks: the factors of a tile are handed over in two chunks (512 + 64); int32
+    partials via the dump entry, fp32 result against float64."""
+    M, N, Kd = 128, 256, 128 * 576
+    g = torch.Generator().manual_seed(43)
+    aq, bq = _randq(g, 1, M, Kd), _randq(g, N, Kd)
+    a_s = torch.rand(1, 1, Kd // 128, generator=g) + 0.5
+    b_s = torch.rand(N, generator=g) + 0.5
+    P = K.gemm_dump_i32(aq.to(DEV), bq.to(DEV), per_block=True)[0].cpu()          # [KB, M, N]
+    ref = (P.double() * a_s[0, 0].double().view(-1, 1, 1)).sum(0) * b_s.double().view(1, N)
+    for b_scale, kind in ((b_s, L.BSCALE_CHANNEL),):
+        fast = K.gemm_block(aq.to(DEV), bq.to(DEV), a_s.to(DEV), b_scale.to(DEV), b_kind=kind, flags=L.GEMM_OUT_F32)[0].cpu().double()
+        assert R.rel_fro(fast, ref) < 1e-4
+    K.check_status(DEV)
