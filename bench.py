@@ -775,6 +775,8 @@ def main():
         dist.barrier()
         torch.cuda.synchronize()
         dist.destroy_process_group()
+    sys.stdout.flush()
+    sys.stderr.flush()
     os._exit(rc)
 
 
