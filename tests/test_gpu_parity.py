@@ -417,3 +417,16 @@ def test_fast_block_epilogue_more_than_512_k_blocks():
         fast = K.gemm_block(aq.to(DEV), bq.to(DEV), a_s.to(DEV), b_scale.to(DEV), b_kind=kind, flags=L.GEMM_OUT_F32)[0].cpu().double()
         assert R.rel_fro(fast, ref) < 1e-4
     K.check_status(DEV)
+
+
+@pytest.mark.parametrize("cols", [384, 8192, 8192 + 384])
+def test_rotated_row_quantizer_both_kernels(cols):
+    """Per-row scale with the 128-point rotation: rows of up to 8192 elements take the kernel that keeps the
+    rotated row in registers, longer rows the two-sweep kernel; both must equal the oracle bit for bit."""
+    g = torch.Generator().manual_seed(cols)
+    w = (torch.randn(160, cols, generator=g) * 0.05).to(torch.bfloat16)
+    w[3] = 0
+    w[7, cols - 1] = 9.0
+    q, s = K.quant_row(w.to(DEV), L.QMODE_TRITON, 128)
+    q_ref, s_ref = R.quant_token(R.hadamard(w, 128))
+    _same(q, q_ref, "rotated row int8"); _same(s, s_ref.view(-1), "rotated row scale")

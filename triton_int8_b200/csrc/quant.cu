@@ -733,6 +733,56 @@ quant_row_kernel(const __nv_bfloat16* __restrict__ x, int64_t cols, int8_t* __re
   }
 }
 
+// Row kernel with the 128-point rotation for rows of at most 8192 elements: the rotated values (already
+// rounded to bf16) stay in registers between the absmax sweep and the quantizing sweep, so the row is read
+// and rotated once instead of twice.  Same arithmetic as quant_row_kernel<MODE, true>, bit for bit.
+template <int MODE>
+__global__ void __launch_bounds__(256)
+quant_row_had128_cached_kernel(const __nv_bfloat16* __restrict__ x, int64_t cols, int8_t* __restrict__ q,
+                               float* __restrict__ scale) {
+  __shared__ float s_red[8];
+  const int tid = threadIdx.x, l = tid & 31;
+  const int64_t row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * cols);
+  const int nchunks = (int)(cols / 8);
+  uint4 cache[4];
+  __nv_bfloat162 hm = __floats2bfloat162_rn(0.f, 0.f);
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int ch = it * 256 + tid;
+    float v[8];
+    if (ch < nchunks) unpack8(__ldg(xr + ch), v);
+    else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    }
+    fwht128_lanes16(v, l);   // whole warps take part: a 128-wide group never straddles the end of the row
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&cache[it]);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      h[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+      hm = __hmax2(hm, __habs2(h[k]));
+    }
+  }
+  float m = fmaxf(__low2float(hm), __high2float(hm));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (l == 0) s_red[tid >> 5] = m;
+  __syncthreads();
+  m = s_red[0];
+#pragma unroll
+  for (int k = 1; k < 8; ++k) m = fmaxf(m, s_red[k]);
+  float s, stored;
+  make_scale<MODE>(m, s, stored);
+  if (tid == 0) scale[row] = stored;
+  uint2* qr = reinterpret_cast<uint2*>(q + row * cols);
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int ch = it * 256 + tid;
+    if (ch < nchunks) qr[ch] = quant_piece<MODE>(cache[it], s);
+  }
+}
+
 // Whole-row Hadamard (power-of-two cols <= 32768): the row lives in shared memory as fp32.
 // Spans 1..64 run in registers/shuffles exactly as above, spans >= 128 as shared-memory passes.
 template <int MODE>
@@ -929,7 +979,8 @@ extern "C" int i8l_quant_row(const void* x, int64_t rows, int64_t cols, int qmod
   if (hadamard != I8L_HAD_NONE && hadamard != I8L_HAD_128) return fail(I8L_ERR_ARG, "bad hadamard=%d", hadamard);
 #define I8L_ROW_CASE(Mo)                                                                              \
   if (qmode == Mo) {                                                                                  \
-    if (hadamard) quant_row_kernel<Mo, true><<<(unsigned)rows, 256, 0, st>>>(xp, cols, q, scale);     \
+    if (hadamard && cols <= 8192) quant_row_had128_cached_kernel<Mo><<<(unsigned)rows, 256, 0, st>>>(xp, cols, q, scale); \
+    else if (hadamard) quant_row_kernel<Mo, true><<<(unsigned)rows, 256, 0, st>>>(xp, cols, q, scale);     \
     else quant_row_kernel<Mo, false><<<(unsigned)rows, 256, 0, st>>>(xp, cols, q, scale);             \
     I8L_CUDA_OK(cudaGetLastError());                                                                  \
     return I8L_OK;                                                                                    \
