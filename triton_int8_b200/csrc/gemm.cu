@@ -4,21 +4,23 @@
 // One persistent CTA per SM, 640 threads:
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      tensor-memory allocator + MMA issuer (one elected lane)
-//   warps 2-3   idle (they complete the first warpgroup so register budgets can be rebalanced)
+//   warp 2      factor warp (fast block-scaled kind): prepares, one tile ahead, the signed per-K-block
+//               factors and the column scales the epilogue needs; idle in the other kinds
+//   warp 3      idle (completes the first warpgroup so register budgets can be rebalanced)
 //   warps 4-19  epilogue: warp%4 selects the 32 accumulator lanes (rows) a warp may read, the
 //               group of four warps selects 64 of the 256 columns of the 128x256 tile.  Sixteen
 //               warps (four per scheduler) because the per-K-block drain is bound by instruction
 //               latency, not by a pipe: more resident warps hide it.
 // Tensor memory holds two 128x256 int32 accumulators (all 512 columns).  In block-scaled mode the
 // MMA warp alternates between them every 128-wide K block while the epilogue drains the other one
-// into fp32 registers (acc += float(P) * scale); in row x column mode a buffer holds a whole tile
-// and the epilogue of tile i overlaps the main loop of tile i+1.
+// into fp32 registers (acc += float(P) * scale; in the fast kind float(P) is formed by an integer add of
+// a magic number whose multiple is kept bounded by alternating signs and removed at the tile end); in
+// row x column mode a buffer holds a whole tile and the epilogue of tile i overlaps the main loop of tile i+1.
 //
 // Every wait on an mbarrier is bounded (a poll count worth about two seconds); on expiry the CTA raises
 // a shared abort flag and reports through the status word.  The producer and the MMA issuer then leave
-// their loops; the epilogue warps, which meet at named barriers, run through their remaining tiles
-// without waiting or computing; copies in flight are awaited, so the kernel always terminates and
-// frees its tensor memory.
+// their loops; the epilogue warps run through their remaining tiles without waiting, computing or
+// storing; copies in flight are awaited, so the kernel always terminates and frees its tensor memory.
 //
 // Scatter mode (i8l_gemm_block_scatter): the epilogue writes each 128-row block into a slot of a
 // buffer owned by another GPU (plain stores to peer-mapped memory), for a reduce-scatter without a
