@@ -103,7 +103,8 @@ I8L_API int i8l_quant_col_t(const void* x, int64_t rows, int64_t cols, int qmode
 /*
  * As i8l_quant_col_t, with a 128-point Walsh-Hadamard rotation along the rows of x (the contraction
  * axis of the transposed operand) in front: W^T of a rotated linear layer's dX GEMM.  Two passes over
- * x (column absmax of the rotated values, then quantise); qmode TRITON or RNE.
+ * x (column absmax of the rotated values, then quantise); qmode TRITON, RNE or ROWRCP (the last one
+ * gives the transposed double_channel operands of a backward pass).
  * No counterpart in the reference.
  */
 I8L_API int i8l_quant_col_t_rot(const void* x, int64_t rows, int64_t cols, int qmode, int8_t* qt,

@@ -109,6 +109,11 @@ def test_quant_row_modes_and_col_t():
     qt, st = K.quant_col_t(w.to(DEV), L.QMODE_TRITON, hadamard=128)   # rotated along the rows of w (N)
     q_ref, s_ref = R.quant_token(R.hadamard(w.t().contiguous(), 128))
     _same(qt, q_ref, "rotated col_t int8"); _same(st, s_ref.view(-1), "rotated col_t scale")
+    for had in (0, 128):   # the double_channel scale (127 / absmax as a reciprocal): transposed operands of its backward
+        qt, st = K.quant_col_t(w.to(DEV), L.QMODE_ROWRCP, hadamard=had)
+        wt = w.t().contiguous()
+        q_ref, s_ref = R.quant_row((R.hadamard(wt, 128) if had else wt)[None])
+        _same(qt, q_ref[0], f"rowrcp col_t int8, hadamard={had}"); _same(st, s_ref.view(-1), "rowrcp col_t scale")
 
 
 @pytest.mark.parametrize("kind", ["tile128", "row128", "rowfull"])

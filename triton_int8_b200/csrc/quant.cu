@@ -1043,6 +1043,7 @@ extern "C" int i8l_quant_col_t_rot(const void* x, int64_t rows, int64_t cols, in
   I8L_CUDA_OK(cudaMemsetAsync(colmax_scratch, 0, (size_t)cols * sizeof(float), st));
   if (qmode == I8L_QMODE_TRITON) return launch_col_t_rot<I8L_QMODE_TRITON>(x, rows, cols, qt, scale_t, colmax_scratch, st);
   if (qmode == I8L_QMODE_RNE) return launch_col_t_rot<I8L_QMODE_RNE>(x, rows, cols, qt, scale_t, colmax_scratch, st);
+  if (qmode == I8L_QMODE_ROWRCP) return launch_col_t_rot<I8L_QMODE_ROWRCP>(x, rows, cols, qt, scale_t, colmax_scratch, st);
   return fail(I8L_ERR_ARG, "i8l_quant_col_t_rot: unsupported qmode=%d", qmode);
 }
 

@@ -89,10 +89,10 @@ def linear_forward(x2: torch.Tensor, weight: torch.Tensor, bias, cfg: Int8Config
 
 def _dc_transposed(t2: torch.Tensor, cfg: Int8Config):
     """t2 bf16 [R, C] -> (int8 t2^T [1, C, R], fp32 scale [1, C]): one scale per column of t2 over all rows.
-    Without rotation the transposing quantizer does it in one pass; a rotation along R goes through a
-    transposed copy and the row quantizer."""
-    if not cfg.hadamard:
-        q, s = K.quant_col_t(t2, L.QMODE_ROWRCP)
+    The transposing quantizer does it without a bf16 transpose, rotated in 128-wide groups along R or not;
+    only a rotation over the whole of R goes through a transposed copy and the row quantizer."""
+    if cfg.hadamard in (0, 128):
+        q, s = K.quant_col_t(t2, L.QMODE_ROWRCP, cfg.hadamard)
         return q[None], s[None]
     return K.quant_row(t2.t().contiguous()[None], L.QMODE_ROWRCP, cfg.hadamard)
 
