@@ -445,12 +445,12 @@ def main():
             gemm_events.append(e)
         return y, dx, dw
 
-    # The step (10 launches, plus the reduce-scatter when sharded) is captured once into a CUDA graph and the
-    # timed region replays it, at every GPU count alike: a host that is slow to issue launches (these machines
-    # are shared; stalls of 40-180 ms inside single steps were seen) then cannot leave the GPU idle inside the
-    # timed region, and 1 GPU and 8 GPUs are timed in the same mode.  The same K steps are timed launch by
-    # launch right afterwards (`launch_by_launch`, with the per-GEMM events).  If the capture fails on any rank
-    # all ranks fall back to launch by launch.
+    # The step (8 launches, plus the reduce-scatter when sharded) is captured once into a CUDA graph and the
+    # timed region replays it, at every GPU count alike: launches issued while nvidia-smi samples the clocks
+    # wait on the driver (stalls of 40-180 ms inside single steps were seen), which a replay avoids, and 1 GPU
+    # and 8 GPUs are timed in the same mode.  The same K steps are timed launch by launch right afterwards
+    # (`launch_by_launch`, with the per-GEMM events) and once more after the sampler has stopped.  If the
+    # capture fails on any rank all ranks fall back to launch by launch.
     def timed(run_one, n):
         t0, t1 = ev(), ev()
         sync_all()
@@ -492,6 +492,9 @@ def main():
             launch_mode = "CUDA graph replay of the whole step"
             ms_graph = timed(graph.replay, args.steps)
         ms_lbl = timed(lambda: step(record=True), args.steps)
+    # the same launch-by-launch pass once more with no nvidia-smi query loop beside it: the difference shows how
+    # much of the launch-by-launch time is the host waiting on the driver while it is being queried
+    ms_lbl_quiet = None if args.lean else timed(step, args.steps)
     ms_per_step = ms_graph if ms_graph is not None else ms_lbl
     tokens_per_s = M / (ms_per_step * 1e-3)
 
@@ -754,7 +757,8 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": workload_config(desc, had, M, K, N, world, reduce_scatter=rs_mode, launch=launch_mode,
                                       l2="inputs (X 0.5 GB + dY >= 0.2 GB per step) exceed the 126 MB L2; no explicit flush"),
-            "launch_by_launch": {"ms_per_step": ms_lbl, "value": M / (ms_lbl * 1e-3)},
+            "launch_by_launch": {"ms_per_step": ms_lbl, "value": M / (ms_lbl * 1e-3),
+                                 "ms_per_step_without_clock_sampling": ms_lbl_quiet},
             "parity": parity,
             "tops_per_gpu": tops, "gemm_ms": {"fwd": t_fwd, "dx": t_dx, "dw": t_dw},
             "roofline": roofline, "targets": targets, "quantizers": quant, "cpu_baseline": cpu_baseline, "e2e": e2e,
