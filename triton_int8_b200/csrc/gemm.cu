@@ -114,6 +114,9 @@ struct __align__(8) SharedCtl {   // tempty must directly follow tfull (the fast
   float fac[2][EPI_WARPS / 4][FAC_MAX];      // signed per-K-block scalar factors
   float fbscale[2][EPI_WARPS / 4][EPI_COLS]; // per-channel column scales (times post_scale)
   float fbias[2][EPI_WARPS / 4][2];          // running sum of the signed factors of the tile (value, error term)
+  // scatter mode of the fast block kind: four output rows x 128 bytes per epilogue warp, staged so that one
+  // store instruction writes whole 128-byte row segments into the peer's memory
+  uint4 xpose[EPI_WARPS][4][8];
 };
 
 // Epilogue kinds.  Everything but K_ROWCOL drains the accumulator every 128-wide K block.
@@ -521,7 +524,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             aph = (gstep >> 1) & 1u;
           }
         }
-        if (active && !*abort_flag) {   // after a timeout the accumulators are not a product: nothing is stored
+        // after a timeout the accumulators are not a product: nothing is stored (decided per warp: the store
+        // path below synchronises the warp)
+        if (active && __all_sync(0xffffffffu, !*abort_flag)) {
           int t2 = t;
           asm volatile("" : "+r"(t2));  // keeps the tile's coordinates out of the K-block loop's live registers
           const TileCoord tc = unit_tile(t2);
@@ -543,7 +548,38 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             cbase = p.c_slots[owner];
             row += (int64_t)(p.rs_rank - owner) * p.rs_rows;
           }
-          store_cols<false>(p, out, chan ? ctl.fbscale[unit & 1][wg] : nullptr, row, tc.n_tile * BN + wg * EPI_COLS, cbase);
+          const float* bsc = chan ? ctl.fbscale[unit & 1][wg] : nullptr;
+          const int col0 = tc.n_tile * BN + wg * EPI_COLS;
+          if (p.rs_rows && !p.out_f32 && !p.bias) {
+            // Peer stores.  A lane owns one row, so a plain store instruction would send 32 separate 32-byte
+            // pieces over NVLink; here the warp passes four rows at a time through shared memory (16-byte
+            // slots, XOR-swizzled so that writers and readers are conflict-free) and every store instruction
+            // then covers four rows x 128 contiguous bytes.  Same values as store_cols.
+            uint32_t w[EPI_COLS / 2];
+#pragma unroll
+            for (int j = 0; j < EPI_COLS / 2; ++j) {
+              float a = out[2 * j], b = out[2 * j + 1];
+              if (bsc) { a *= bsc[2 * j]; b *= bsc[2 * j + 1]; }
+              w[j] = pack_bf16x2(a, b);
+            }
+            uint4* xp = &ctl.xpose[warp - 4][0][0];
+            const int wr = lane & 3, rr = lane >> 3, rc = lane & 7;
+            __nv_bfloat16* obase = static_cast<__nv_bfloat16*>(cbase) + (row - lane) * p.N + col0 + rc * 8;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if ((lane >> 2) == j) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                  xp[wr * 8 + (c ^ (wr << 1))] = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+              }
+              __syncwarp();
+              const uint4 v = xp[rr * 8 + (rc ^ (rr << 1))];
+              *reinterpret_cast<uint4*>(obase + (int64_t)(4 * j + rr) * p.N) = v;
+              __syncwarp();
+            }
+          } else {
+            store_cols<false>(p, out, bsc, row, col0, cbase);
+          }
         }
         mbar_arrive(smem_u32(&ctl.ffree[unit & 1]));   // this tile's factors and column scales are no longer needed
         ++unit;
