@@ -236,8 +236,9 @@ def main():
     ap.add_argument("--reduce-scatter", default="nccl", choices=["peer", "nccl"],
                     help="N>1: dX partials scattered by the GEMM epilogue into peer memory (default; falls back to\n"
                          "nccl when the peer mapping cannot be set up), or a separate NCCL reduce-scatter")
-    ap.add_argument("--comm-sms", type=int, default=16,
-                    help="N>1: SMs the dW GEMM leaves to the NCCL reduce-scatter that runs beside it (0 = none)")
+    ap.add_argument("--comm-sms", type=int, default=None,
+                    help="N>1: SMs the dW GEMM leaves to the NCCL reduce-scatter that runs beside it (0 = none; "
+                         "default: the library's choice by world size, 16 up to 4 GPUs and 32 from 8)")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time the step launch by launch even on one GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -756,6 +757,7 @@ def main():
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": workload_config(desc, had, M, K, N, world, reduce_scatter=rs_mode, launch=launch_mode,
+                                      sms_left_to_the_collective=(step_obj.comm_sms if world > 1 and peer_slots is None else 0),
                                       l2="inputs (X 0.5 GB + dY >= 0.2 GB per step) exceed the 126 MB L2; no explicit flush"),
             "launch_by_launch": {"ms_per_step": ms_lbl, "value": M / (ms_lbl * 1e-3),
                                  "ms_per_step_without_clock_sampling": ms_lbl_quiet},

@@ -176,12 +176,20 @@ class ColumnParallelStep:
     """Forward + backward of one column-parallel linear with the dX reduce-scatter overlapped
     with the dW GEMM.  Holds the side stream and events; reuse one instance per layer."""
 
-    def __init__(self, group=None, cfg: Int8Config = DEFAULT, peer_slots: PeerSlots | None = None, comm_sms: int = 16):
+    def __init__(self, group=None, cfg: Int8Config = DEFAULT, peer_slots: PeerSlots | None = None,
+                 comm_sms: int | None = None):
         self.group, self.cfg = group, cfg
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.comm_stream = torch.cuda.Stream() if self.world > 1 else None
         # The GEMMs are persistent, one CTA per SM; the dW GEMM that runs beside the reduce-scatter leaves
-        # `comm_sms` SMs to the collective's CTAs (otherwise NCCL's kernel waits for the GEMM to end).
+        # `comm_sms` SMs to the collective's CTAs (otherwise NCCL's kernel waits for the GEMM to end).  The
+        # reduce-scatter moves about the same bytes per rank at every world size while the dW GEMM beside it
+        # shrinks with 1/world, so the collective needs more SMs as the group grows; measured on the
+        # M=32768, K=8192, N=28672 layer: 16 is best at 4 ranks (0 / 16 / 32 SMs: 7.79 / 7.39 / 7.55 ms per
+        # step), 32 at 8 ranks (4.48 / 4.35 / 3.94 ms).  None picks by world size.
+        if comm_sms is None:
+            comm_sms = 32 if self.world >= 8 else 16
+        self.comm_sms = comm_sms
         sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
         self.dw_ctas = max(1, sms - comm_sms) if (self.world > 1 and comm_sms > 0) else 0
         self.peer_slots = peer_slots   # when given, the dX GEMM scatters its partials itself (no NCCL reduce-scatter)
