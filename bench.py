@@ -238,7 +238,7 @@ def main():
                          "nccl when the peer mapping cannot be set up), or a separate NCCL reduce-scatter")
     ap.add_argument("--comm-sms", type=int, default=None,
                     help="N>1: SMs the dW GEMM leaves to the NCCL reduce-scatter that runs beside it (0 = none; "
-                         "default: the library's choice by world size, 16 up to 4 GPUs and 32 from 8)")
+                         "default: the library's choice, 4 per GPU of the group, between 8 and 32)")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time the step launch by launch even on one GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")

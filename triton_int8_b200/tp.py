@@ -185,10 +185,11 @@ class ColumnParallelStep:
         # `comm_sms` SMs to the collective's CTAs (otherwise NCCL's kernel waits for the GEMM to end).  The
         # reduce-scatter moves about the same bytes per rank at every world size while the dW GEMM beside it
         # shrinks with 1/world, so the collective needs more SMs as the group grows; measured on the
-        # M=32768, K=8192, N=28672 layer: 16 is best at 4 ranks (0 / 16 / 32 SMs: 7.79 / 7.39 / 7.55 ms per
-        # step), 32 at 8 ranks (4.48 / 4.35 / 3.94 ms).  None picks by world size.
+        # M=32768, K=8192, N=28672 layer: 8 at 2 ranks (8 / 16 SMs: 14.2 / 14.5 ms per step), 16 at 4 ranks
+        # (0 / 16 / 32 SMs: 7.79 / 7.39 / 7.55 ms), 32 at 8 ranks (0 / 16 / 24 / 32 / 48 SMs: 4.48 / 4.35 /
+        # 4.40 / 3.94 / 4.01 ms).  None picks 4 SMs per rank, between 8 and 32.
         if comm_sms is None:
-            comm_sms = 32 if self.world >= 8 else 16
+            comm_sms = min(32, max(8, 4 * self.world))
         self.comm_sms = comm_sms
         sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
         self.dw_ctas = max(1, sms - comm_sms) if (self.world > 1 and comm_sms > 0) else 0
